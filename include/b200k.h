@@ -1,0 +1,149 @@
+/*
+ * b200k.h -- C ABI of libb200k.so: hand-written sm_100a kernels behind the
+ * reference's two torch-extension packages (gemm_unified, fmha_unified).
+ *
+ * Plain pointers and sizes only: no torch types cross this boundary.  Every
+ * pointer named "device" is a CUDA device pointer owned by the caller; the
+ * library never frees caller memory and launches on the stream it is given
+ * (0 = the legacy default stream) without synchronising the host.
+ *
+ * All functions return B200K_OK (0) or a negative B200K_E* code;
+ * b200k_strerror() maps a code to text.  A kernel whose bounded device-side
+ * wait expired does not trap: it records a status word that
+ * b200k_device_status() reads back after the stream was synchronised.
+ */
+#ifndef B200K_H_
+#define B200K_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* opaque stream handle: pass a cudaStream_t (or torch's stream.cuda_stream) */
+typedef void* b200k_stream_t;
+
+enum {
+  B200K_OK = 0,
+  B200K_EDTYPE = -1,     /* dtype is not B200K_F16 / B200K_BF16 */
+  B200K_ESHAPE = -2,     /* negative / zero / inconsistent extents */
+  B200K_EALIGN = -3,     /* base pointer or leading dimension breaks the 16-byte rule of TMA */
+  B200K_EHEADDIM = -4,   /* head_dim other than 64 or 128 */
+  B200K_EWORKSPACE = -5, /* workspace missing or too small */
+  B200K_ECUDA = -6,      /* a CUDA runtime / driver call failed */
+  B200K_ETIMEOUT = -7,   /* a bounded device-side wait expired (see b200k_device_status) */
+  B200K_ETMAP = -8,      /* cuTensorMapEncodeTiled refused the operand */
+  B200K_EARG = -9,       /* other invalid argument (e.g. causal together with decode) */
+  B200K_ENOGPU = -10     /* no sm_100 device is current */
+};
+
+enum { B200K_F16 = 0, B200K_BF16 = 1 };
+
+/* GEMM kernel variants (the `variant` argument of b200k_gemm). */
+enum {
+  B200K_GEMM_AUTO = 0,      /* heuristic: picks one of the below from M, N, K */
+  B200K_GEMM_1CTA = 1,      /* 128x256x64 tiles, one CTA per tile, persistent, warp-specialised */
+  B200K_GEMM_2CTA = 2,      /* 256x256x64 tiles on a CTA pair (cta_group::2) */
+  B200K_GEMM_SKINNY = 3,    /* M <= 128: weight-streaming split-K path */
+  B200K_GEMM_1CTA_N128 = 4, /* 128x128x64 tiles: more CTAs for small problems */
+  B200K_GEMM_GENERIC = 5    /* CUDA-core kernel without alignment rules (any M, N, K, ld) */
+};
+
+/*
+ * C[M,N] = A[M,K] . B[K,N]; A, B, C row-major with leading dimensions lda,
+ * ldb, ldc in ELEMENTS; fp16 or bf16 in and out, fp32 accumulation.
+ * Replaces the host launchers `at::Tensor finegemm_N(const at::Tensor& a,
+ * const at::Tensor& b)` of the reference
+ * (kernels/gemm/pkg/gemm_unified/csrc/semi/gemm_11_nv.cu:175-216,
+ *  kernels/gemm/pkg/gemm_unified/csrc/manual/gemm_12_nv.cu:33-103,
+ *  kernels/gemm/pkg/gemm_unified/csrc/auto/gemm_0.cu:23-47), whose
+ * contract is a[i*K+k], b[k*N+j], c[i*N+j] (auto/gemm_0.cu:12-20).
+ * The tensor-core variants need 16-byte aligned bases and lda, ldb, ldc
+ * multiples of 8 elements; AUTO falls back to GENERIC otherwise.
+ * `workspace` is only used by B200K_GEMM_SKINNY (split-K partial sums, see
+ * b200k_gemm_workspace_bytes); it may be NULL for the other variants.
+ */
+int b200k_gemm(const void* A_device, const void* B_device, void* C_device,
+               int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+               int dtype, int variant,
+               void* workspace_device, size_t workspace_bytes,
+               b200k_stream_t stream);
+
+/* Bytes of workspace b200k_gemm needs for (M,N,K,variant); 0 when none. */
+size_t b200k_gemm_workspace_bytes(int M, int N, int K, int variant);
+
+/*
+ * Fused multi-head attention forward, O = softmax(Q K^T * scale + mask) V,
+ * online softmax in fp32, GQA by kv_head = q_head / (Hq / Hkv).
+ * Q, O: [B, Hq, Sq, D]; K, V: [B, Hkv, Skv, D] addressed through
+ * (batch, head, row) strides in ELEMENTS, the D axis contiguous.  So both the
+ * reference's "bhsd" tensors and "bshd" storage are taken without a copy.
+ * causal != 0 masks key j for query i when j > i + (Skv - Sq) (identical to the
+ * reference's top-left rule `q_idx < k_idx` when Sq == Skv).
+ * kv_len (0 < kv_len <= Skv) masks keys j >= kv_len.
+ * Replaces `torch::Tensor finefmha_N(Q, K, V, causal, is_decode,
+ * decode_length)` of the reference
+ * (kernels/fmha/pkg/fmha_unified/csrc/semi/fmha_4_nv.cu:395-443,
+ *  kernels/fmha/pkg/fmha_unified/csrc/manual/fmha_5_nv.cu:135-187).
+ */
+int b200k_fmha_fwd(const void* Q_device, const void* K_device, const void* V_device,
+                   void* O_device,
+                   int B, int Hq, int Hkv, int Sq, int Skv, int D,
+                   const int64_t q_strides[3], const int64_t k_strides[3],
+                   const int64_t v_strides[3], const int64_t o_strides[3],
+                   float scale, int causal, int kv_len, int dtype, int variant,
+                   b200k_stream_t stream);
+
+/*
+ * Decode-shaped attention (few query rows per sequence, normally Sq == 1)
+ * with the key/value range of every (batch, kv-head) cut into `num_splits`
+ * chunks that run on different CTAs, followed by a reduction kernel that
+ * merges the per-chunk (max, sum, partial O) triples in a fixed order.
+ * kv_lens_device: int32[B] on the device with the valid length of each
+ * sequence, or NULL for Skv everywhere.  num_splits = 0 lets the library
+ * choose.  The workspace holds the partial triples
+ * (b200k_fmha_decode_workspace_bytes).
+ * Has the same reference counterpart as b200k_fmha_fwd with is_decode = true
+ * (kernels/fmha/pkg/fmha_unified/csrc/semi/fmha_4_nv.cu:240-243,415-417); the
+ * per-sequence length vector is an addition, the reference passes one scalar
+ * `decode_length` (kernels/fmha/pkg/fmha_unified/ops.py:18).
+ */
+int b200k_fmha_decode_splitkv(const void* Q_device, const void* K_device,
+                              const void* V_device, void* O_device,
+                              int B, int Hq, int Hkv, int Sq, int Skv, int D,
+                              const int64_t q_strides[3], const int64_t k_strides[3],
+                              const int64_t v_strides[3], const int64_t o_strides[3],
+                              float scale, const int32_t* kv_lens_device,
+                              int num_splits, int dtype,
+                              void* workspace_device, size_t workspace_bytes,
+                              b200k_stream_t stream);
+
+size_t b200k_fmha_decode_workspace_bytes(int B, int Hq, int Hkv, int Sq, int Skv, int D,
+                                         int num_splits);
+
+/* The split count b200k_fmha_decode_splitkv uses for num_splits = 0. */
+int b200k_fmha_decode_auto_splits(int B, int Hkv, int Skv);
+
+/* Text for a return code. */
+const char* b200k_strerror(int code);
+
+/*
+ * Reads (and clears) the device status word of the current device.  Call after
+ * the stream was synchronised.  *code_out: 0 or B200K_ETIMEOUT; *detail_out:
+ * (kernel id << 24) | (role << 16) | block index of the first CTA that gave up.
+ * Synchronises the device.
+ */
+int b200k_device_status(int* code_out, int* detail_out);
+
+/* Number of kernels this library has launched in this process (all entry points). */
+uint64_t b200k_launch_count(void);
+
+/* 1 when the current device is compute capability 10.x, else 0. */
+int b200k_device_supported(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200K_H_ */

@@ -1,0 +1,92 @@
+"""ctypes binding of libb200k.so (the C ABI declared in include/b200k.h).
+
+There is no fallback: if the library is missing, or the device is not an
+sm_100 GPU, every call raises.  The host side stays Python/PyTorch exactly as
+in the reference (kernels/gemm/pkg/gemm_unified/ops.py:7-13 and
+kernels/fmha/pkg/fmha_unified/ops.py:8-29 are Python wrappers over C++ ops);
+torch is used for device memory and streams only.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint64, c_void_p, POINTER
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent.parent
+LIB_PATH = Path(os.environ.get("B200K_LIB", PKG_DIR / "lib" / "libb200k.so"))
+
+F16, BF16 = 0, 1
+
+# every symbol include/b200k.h declares, with its ctypes signature
+_I64x3 = POINTER(c_int64)
+SIGNATURES = {
+    "b200k_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
+                           c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "b200k_gemm_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "b200k_fmha_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                               _I64x3, _I64x3, _I64x3, _I64x3, c_float, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200k_fmha_decode_splitkv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                          c_int, c_int, _I64x3, _I64x3, _I64x3, _I64x3, c_float, c_void_p,
+                                          c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "b200k_fmha_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
+    "b200k_fmha_decode_auto_splits": (c_int, [c_int, c_int, c_int]),
+    "b200k_strerror": (c_char_p, [c_int]),
+    "b200k_device_status": (c_int, [POINTER(c_int), POINTER(c_int)]),
+    "b200k_launch_count": (c_uint64, []),
+    "b200k_device_supported": (c_int, []),
+}
+
+
+class B200KError(RuntimeError):
+    """A libb200k entry point returned a negative code."""
+
+    def __init__(self, code: int, where: str):
+        self.code = code
+        super().__init__(f"{where}: {strerror(code)} (code {code})")
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads libb200k.so once; raises if it was not built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python {PKG_DIR / 'build.py'}` "
+                "(there is no CPU or eager fallback)")
+        handle = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def strerror(code: int) -> str:
+    return lib().b200k_strerror(code).decode()
+
+
+def check(code: int, where: str) -> None:
+    if code != 0:
+        raise B200KError(code, where)
+
+
+def launch_count() -> int:
+    return int(lib().b200k_launch_count())
+
+
+def device_status() -> tuple[int, int]:
+    """(code, detail) of the current device's status word; synchronises."""
+    code, detail = c_int(0), c_int(0)
+    check(lib().b200k_device_status(ctypes.byref(code), ctypes.byref(detail)), "b200k_device_status")
+    return code.value, detail.value
+
+
+def strides3(t) -> ctypes.Array:
+    """(batch, head, row) element strides of a [B, H, S, D] tensor as int64[3]."""
+    s = t.stride()
+    return (c_int64 * 3)(s[0], s[1], s[2])

@@ -1,0 +1,54 @@
+"""Tensor-level wrapper of b200k_gemm."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+AUTO, ONE_CTA, TWO_CTA, SKINNY, ONE_CTA_N128, GENERIC = 0, 1, 2, 3, 4, 5
+
+_DTYPES = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+
+
+def _check_inputs(a: torch.Tensor, b: torch.Tensor) -> None:
+    # same conditions, in the same order, as the reference launchers
+    # (kernels/gemm/pkg/gemm_unified/csrc/auto/gemm_0.cu:25-31), plus bf16
+    if a.dim() != 2 or b.dim() != 2:
+        raise RuntimeError("a and b must be 2-D")
+    if a.size(1) != b.size(0):
+        raise RuntimeError(f"shape mismatch: a is {tuple(a.shape)}, b is {tuple(b.shape)}")
+    if a.dtype not in _DTYPES or b.dtype != a.dtype:
+        raise RuntimeError(f"a and b must both be float16 or bfloat16, got {a.dtype} and {b.dtype}")
+    if not a.is_cuda or not b.is_cuda:
+        raise RuntimeError("a and b must be CUDA tensors")
+    if a.device != b.device:
+        raise RuntimeError("a and b must be on the same device")
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, variant: int = AUTO) -> torch.Tensor:
+    """C = a @ b with fp32 accumulation on the sm_100a kernels; a [M,K], b [K,N] row-major."""
+    _check_inputs(a, b)
+    if a.stride(1) != 1:
+        a = a.contiguous()
+    if b.stride(1) != 1:
+        b = b.contiguous()
+    M, K = a.shape
+    N = b.size(1)
+    if out is None:
+        out = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    elif out.shape != (M, N) or out.dtype != a.dtype or out.device != a.device or out.stride(1) != 1:
+        raise RuntimeError("out has the wrong shape, dtype, device or layout")
+    if M == 0 or N == 0:
+        return out
+    if K == 0:
+        return out.zero_()
+    L = _lib.lib()
+    with torch.cuda.device(a.device):
+        ws_bytes = L.b200k_gemm_workspace_bytes(M, N, K, variant)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device) if ws_bytes else None
+        code = L.b200k_gemm(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K,
+                            a.stride(0), b.stride(0), out.stride(0), _DTYPES[a.dtype], variant,
+                            ws.data_ptr() if ws is not None else None, ws_bytes,
+                            torch.cuda.current_stream(a.device).cuda_stream)
+    _lib.check(code, "b200k_gemm")
+    return out

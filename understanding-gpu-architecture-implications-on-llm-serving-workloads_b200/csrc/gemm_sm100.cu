@@ -1,0 +1,425 @@
+// C[M,N] = A[M,K] . B[K,N], row-major, fp16/bf16 in and out, fp32 accumulate.
+//
+// Tensor-core path (one CTA per 128 x BN output tile, persistent):
+//   warp 0      TMA producer: A box 64(K) x 128(M), B boxes 64(N) x 64(K), 128-byte swizzle,
+//               STAGES-deep ring guarded by full/empty mbarriers
+//   warp 1      MMA issuer: tcgen05.mma kind::f16, M = 128, N = BN, K = 16, A K-major,
+//               B MN-major (B is row-major [K,N], so N is the contiguous axis);
+//               accumulator double-buffered in TMEM (2 x BN columns)
+//   warps 2..5  epilogue: tcgen05.ld -> fp32 -> 16-bit -> swizzled smem -> TMA store,
+//               overlapping the next tile's main loop
+// Ragged M, N, K edges are handled by TMA: loads outside the tensor read zero,
+// stores outside are clipped.
+//
+// Reference contract: kernels/gemm/pkg/gemm_unified/csrc/auto/gemm_0.cu:12-20
+// (a[i*K+k], b[k*N+j], c[i*N+j]); reference launchers e.g.
+// kernels/gemm/pkg/gemm_unified/csrc/semi/gemm_11_nv.cu:175-216.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace b200k {
+
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kGemmThreads = 192;
+constexpr int kGroupN = 8;  // n-blocks per rasterisation group
+
+// Tile order: groups of kGroupN n-blocks, m fastest across the group, so the CTAs
+// resident at one time share few A row-slabs and few B column-slabs in L2.
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb, int& nb) {
+  const int per_group = kGroupN * num_m;
+  const int g = t / per_group;
+  const int first_n = g * kGroupN;
+  const int gsz = min(kGroupN, num_n - first_n);
+  const int r = t - g * per_group;
+  nb = first_n + r % gsz;
+  mb = r / gsz;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr uint32_t kABytes = kBM * kBK * 2;
+  static constexpr uint32_t kBBytes = BN * kBK * 2;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kStagingBytes = 4 * 2 * 4096;  // 4 epilogue warps x 2 buffers x (32 rows x 128 B)
+  static constexpr uint32_t kBarOffset = STAGES * kStageBytes + kStagingBytes;
+  static constexpr uint32_t kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
+};
+
+template <int BN, int STAGES, bool BF16>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_1cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int* status) {
+  using L = GemmSmem<BN, STAGES>;
+  constexpr uint32_t kTmemCols = 2 * BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* staging = smem + STAGES * L::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_m = (M + kBM - 1) / kBM;
+  const int num_n = (N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 4);
+    }
+    fence_mbar_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    prefetch_tmap(&tmC);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(tmem_holder, kTmemCols);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (elect_one()) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int mb, nb;
+        tile_coords(t, num_m, num_n, mb, nb);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            report_timeout(status, KID_GEMM, ROLE_PRODUCER);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * L::kStageBytes;
+          uint8_t* sb = sa + L::kABytes;
+          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+          tma_load_2d(sa, &tmA, &full_bar[stage], kb * kBK, mb * kBM);
+#pragma unroll
+          for (int j = 0; j < BN / 64; ++j)
+            tma_load_2d(sb + j * (kBK * 128), &tmB, &full_bar[stage], nb * BN + j * 64, kb * kBK);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_f16(BF16 ? 1 : 0, /*a K-major*/ 0, /*b MN-major*/ 1, kBM, BN);
+      uint32_t stage = 0, phase = 0;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const uint32_t acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) {
+          report_timeout(status, KID_GEMM, ROLE_MMA);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) {
+            report_timeout(status, KID_GEMM, ROLE_MMA);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t b_addr = a_addr + L::kABytes;
+          // A: K-major, rows of 128 B, 8-row groups 1024 B apart.
+          // B: MN-major, 64 n per 128-B row, 8 k-rows per 1024-B group (stride offset),
+          //    next 64-wide n block kBK*128 B further (leading offset).
+          const uint64_t adesc = make_smem_desc_sw128(a_addr, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(b_addr, kBK * 128, 1024);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            // advance 16 k: A by 32 B inside the swizzled row, B by 16 rows of 128 B
+            umma_ss<1>(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), idesc,
+                       (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit<1>(&empty_bar[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit<1>(&tmem_full[acc]);
+      }
+    }
+  } else {
+    // -------------------------------- epilogue --------------------------------
+    const int ew = warp & 3;  // TMEM lane quadrant this warp may read
+    uint8_t* stg = staging + ew * 8192;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      int mb, nb;
+      tile_coords(t, num_m, num_n, mb, nb);
+      const uint32_t acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_phase)) {
+        if (lane == 0) report_timeout(status, KID_GEMM, ROLE_EPILOGUE);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int row0 = mb * kBM + ew * 32;
+#pragma unroll 1
+      for (int c = 0; c < BN / 64; ++c) {
+        uint32_t v[32], w[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + acc * BN + c * 64;
+        tmem_ld32(taddr, v);
+        tmem_ld32(taddr + 32, w);
+        tmem_ld_wait();
+        uint8_t* buf = stg + (c & 1) * 4096;
+        if (lane == 0) tma_store_wait_read<1>();  // the store that last read `buf` has drained
+        __syncwarp();
+        uint8_t* rowp = buf + lane * 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 q;
+          q.x = pack2<BF16>(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+          q.y = pack2<BF16>(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+          q.z = pack2<BF16>(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+          q.w = pack2<BF16>(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+          *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = q;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 q;
+          q.x = pack2<BF16>(__uint_as_float(w[8 * j + 0]), __uint_as_float(w[8 * j + 1]));
+          q.y = pack2<BF16>(__uint_as_float(w[8 * j + 2]), __uint_as_float(w[8 * j + 3]));
+          q.z = pack2<BF16>(__uint_as_float(w[8 * j + 4]), __uint_as_float(w[8 * j + 5]));
+          q.w = pack2<BF16>(__uint_as_float(w[8 * j + 6]), __uint_as_float(w[8 * j + 7]));
+          *reinterpret_cast<uint4*>(rowp + (((j + 4) ^ (lane & 7)) << 4)) = q;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        const int col0 = nb * BN + c * 64;
+        if (lane == 0 && row0 < M && col0 < N) {
+          tma_store_2d(&tmC, buf, col0, row0);
+          tma_store_commit();
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// CUDA-core kernel without alignment rules (any M, N, K and leading dimensions).
+// 64 x 64 tile, 16-deep k slabs in shared memory, 4 x 4 outputs per thread.
+// ---------------------------------------------------------------------------
+template <bool BF16>
+__device__ __forceinline__ float load16(const void* p, int64_t i) {
+  if constexpr (BF16)
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+  else
+    return __half2float(reinterpret_cast<const __half*>(p)[i]);
+}
+template <bool BF16>
+__device__ __forceinline__ void store16(void* p, int64_t i, float v) {
+  if constexpr (BF16)
+    reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+  else
+    reinterpret_cast<__half*>(p)[i] = __float2half_rn(v);
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+gemm_generic_kernel(const void* __restrict__ A, const void* __restrict__ B, void* __restrict__ C, int M, int N, int K,
+                    int64_t lda, int64_t ldb, int64_t ldc) {
+  __shared__ float sA[16][64 + 1];
+  __shared__ float sB[16][64 + 1];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+      const int r = i >> 4, kk = i & 15;  // A: row r, k kk
+      const int gm = m0 + r, gk = k0 + kk;
+      sA[kk][r] = (gm < M && gk < K) ? load16<BF16>(A, (int64_t)gm * lda + gk) : 0.f;
+      const int kr = i >> 6, c = i & 63;  // B: k kr, col c
+      const int gk2 = k0 + kr, gn = n0 + c;
+      sB[kr][c] = (gk2 < K && gn < N) ? load16<BF16>(B, (int64_t)gk2 * ldb + gn) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = sA[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = sB[kk][tx + 16 * j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int gm = m0 + ty * 4 + i;
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx + 16 * j;
+      if (gn < N) store16<BF16>(C, (int64_t)gm * ldc + gn, acc[i][j]);
+    }
+  }
+}
+
+template <int BN, int STAGES, bool BF16>
+int launch_1cta(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                cudaStream_t stream) {
+  using L = GemmSmem<BN, STAGES>;
+  auto kfn = gemm_1cta_kernel<BN, STAGES, BF16>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev & 63]) {
+    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return B200K_ECUDA;
+    }
+    configured[dev & 63] = true;
+  }
+  CUtensorMap tmA, tmB, tmC;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {kBK, kBM};
+    int r = encode_tmap_16bit(&tmA, A, 2, dims, str, box, true);
+    if (r) return r;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {64, kBK};
+    int r = encode_tmap_16bit(&tmB, B, 2, dims, str, box, true);
+    if (r) return r;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
+    uint64_t str[1] = {(uint64_t)ldc * 2};
+    uint32_t box[2] = {64, 32};
+    int r = encode_tmap_16bit(&tmC, C, 2, dims, str, box, true);
+    if (r) return r;
+  }
+  int* status = status_ptr();
+  if (!status) return B200K_ECUDA;
+  const int num_tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
+  const int sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
+  const int grid = num_tiles < sms ? num_tiles : sms;
+  kfn<<<grid, kGemmThreads, L::kTotal, stream>>>(tmA, tmB, tmC, M, N, K, status);
+  count_launch();
+  return check_launch();
+}
+
+template <bool BF16>
+int launch_generic(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                   cudaStream_t stream) {
+  dim3 grid((N + 63) / 64, (M + 63) / 64);
+  gemm_generic_kernel<BF16><<<grid, 256, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc);
+  count_launch();
+  return check_launch();
+}
+
+}  // namespace
+
+}  // namespace b200k
+
+using namespace b200k;
+
+extern "C" size_t b200k_gemm_workspace_bytes(int M, int N, int K, int variant) {
+  (void)M;
+  (void)N;
+  (void)K;
+  (void)variant;
+  return 0;
+}
+
+extern "C" int b200k_gemm(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                          int64_t ldc, int dtype, int variant, void* workspace, size_t workspace_bytes,
+                          b200k_stream_t stream_) {
+  (void)workspace;
+  (void)workspace_bytes;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (dtype != B200K_F16 && dtype != B200K_BF16) return B200K_EDTYPE;
+  if (M <= 0 || N <= 0 || K <= 0 || lda < K || ldb < N || ldc < N) return B200K_ESHAPE;
+  if (!A || !B || !C) return B200K_EARG;
+  if (!b200k_device_supported()) return B200K_ENOGPU;
+  const bool tma_ok = aligned16(A) && aligned16(B) && aligned16(C) && lda % 8 == 0 && ldb % 8 == 0 && ldc % 8 == 0;
+  if (variant == B200K_GEMM_AUTO) {
+    if (!tma_ok) {
+      variant = B200K_GEMM_GENERIC;
+    } else {
+      const int sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
+      const long tiles256 = (long)((M + 127) / 128) * ((N + 255) / 256);
+      variant = tiles256 >= sms ? B200K_GEMM_1CTA : B200K_GEMM_1CTA_N128;
+    }
+  }
+  const bool bf16 = dtype == B200K_BF16;
+  switch (variant) {
+    case B200K_GEMM_1CTA:
+    case B200K_GEMM_2CTA:
+    case B200K_GEMM_SKINNY:
+      if (!tma_ok) return B200K_EALIGN;
+      return bf16 ? launch_1cta<256, 4, true>(A, B, C, M, N, K, lda, ldb, ldc, stream)
+                  : launch_1cta<256, 4, false>(A, B, C, M, N, K, lda, ldb, ldc, stream);
+    case B200K_GEMM_1CTA_N128:
+      if (!tma_ok) return B200K_EALIGN;
+      return bf16 ? launch_1cta<128, 6, true>(A, B, C, M, N, K, lda, ldb, ldc, stream)
+                  : launch_1cta<128, 6, false>(A, B, C, M, N, K, lda, ldb, ldc, stream);
+    case B200K_GEMM_GENERIC:
+      return bf16 ? launch_generic<true>(A, B, C, M, N, K, lda, ldb, ldc, stream)
+                  : launch_generic<false>(A, B, C, M, N, K, lda, ldb, ldc, stream);
+    default:
+      return B200K_EARG;
+  }
+}

@@ -1,0 +1,151 @@
+// Host-side helpers: tensor-map encoding, device status word, error strings.
+#include "host_common.h"
+
+#include <atomic>
+#include <mutex>
+
+namespace b200k {
+
+namespace {
+constexpr int kMaxDevices = 64;
+
+// status word of each device: [0] code, [1] detail, [2..3] spare
+__device__ int g_status[4];
+
+std::atomic<uint64_t> g_launches{0};
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      return (EncodeTiledFn) nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+}  // namespace
+
+int encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return B200K_ECUDA;
+  cuuint64_t gdims[5];
+  cuuint64_t gstrides[4];
+  cuuint32_t gbox[5];
+  cuuint32_t estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+    estr[i] = 1;
+    if (i + 1 < rank) gstrides[i] = strides_bytes[i];
+  }
+  // BFLOAT16 and FLOAT16 only differ in how an out-of-range fill would be
+  // interpreted; both tile 2-byte elements and the fill used here is zero.
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdims, gstrides,
+                  gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200K_OK : B200K_ETMAP;
+}
+
+int* status_ptr() {
+  static int* ptrs[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ptrs[dev]) {
+    int* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    ptrs[dev] = p;
+  }
+  return ptrs[dev];
+}
+
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+int check_launch() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? B200K_OK : B200K_ECUDA;
+}
+
+const DevInfo& dev_info() {
+  static DevInfo infos[kMaxDevices];
+  static bool have[kMaxDevices] = {};
+  static std::mutex mu;
+  static DevInfo none{0, 0, 0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    (void)cudaGetLastError();
+    return none;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!have[dev]) {
+    DevInfo d{};
+    cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+    cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    infos[dev] = d;
+    have[dev] = true;
+  }
+  return infos[dev];
+}
+
+}  // namespace b200k
+
+extern "C" {
+
+const char* b200k_strerror(int code) {
+  switch (code) {
+    case B200K_OK: return "ok";
+    case B200K_EDTYPE: return "unsupported dtype (expected fp16 or bf16)";
+    case B200K_ESHAPE: return "invalid or inconsistent shape";
+    case B200K_EALIGN: return "pointer or leading dimension not 16-byte aligned";
+    case B200K_EHEADDIM: return "unsupported head_dim (expected 64 or 128)";
+    case B200K_EWORKSPACE: return "workspace missing or too small";
+    case B200K_ECUDA: return "CUDA call failed";
+    case B200K_ETIMEOUT: return "a bounded device-side wait expired";
+    case B200K_ETMAP: return "tensor map encoding failed";
+    case B200K_EARG: return "invalid argument";
+    case B200K_ENOGPU: return "no sm_100 device is current";
+    default: return "unknown b200k error";
+  }
+}
+
+int b200k_device_status(int* code_out, int* detail_out) {
+  int* p = b200k::status_ptr();
+  if (!p) return B200K_ECUDA;
+  if (cudaDeviceSynchronize() != cudaSuccess) return B200K_ECUDA;
+  int host[4] = {0, 0, 0, 0};
+  if (cudaMemcpy(host, p, sizeof(host), cudaMemcpyDeviceToHost) != cudaSuccess) return B200K_ECUDA;
+  if (host[0] != 0) {
+    if (cudaMemset(p, 0, sizeof(host)) != cudaSuccess) return B200K_ECUDA;
+  }
+  if (code_out) *code_out = host[0];
+  if (detail_out) *detail_out = host[1];
+  return B200K_OK;
+}
+
+uint64_t b200k_launch_count(void) { return b200k::g_launches.load(std::memory_order_relaxed); }
+
+int b200k_device_supported(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return b200k::dev_info().cc_major == 10 ? 1 : 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,38 @@
+// Host-side helpers shared by the entry points: tensor-map encoding through
+// the driver entry point (the library does not link libcuda), the per-device
+// status word, launch counting and argument checks.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/b200k.h"
+
+namespace b200k {
+
+// 16-bit element tensor map.  dims/strides innermost first; strides_bytes[i] is
+// the byte stride of dimension i+1 (dimension 0 is contiguous).
+// Returns B200K_OK / B200K_ETMAP / B200K_ECUDA.
+int encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128);
+
+// Device pointer to the int[4] status word of the current device.
+int* status_ptr();
+
+void count_launch(int n = 1);
+
+// Last CUDA error -> B200K_ECUDA (and clears it), else B200K_OK.
+int check_launch();
+
+// properties of the current device, cached per device
+struct DevInfo {
+  int sm_count;
+  int cc_major;
+  int max_smem_optin;
+};
+const DevInfo& dev_info();
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace b200k
