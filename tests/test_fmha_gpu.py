@@ -1,0 +1,156 @@
+"""GPU parity of the FMHA forward path against the CPU oracle, through the C ABI
+(b200k_fmha_fwd via ctypes) and the reference-facing op (fmha_unified.ops.fine_fmha).
+Tolerance: max-abs <= 2e-3 against fp32 softmax(QK^T scale)V for N(0,1) inputs
+(the stated bar)."""
+import pytest
+import torch
+
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL = oracle.FMHA_MAX_ABS_TOL
+
+
+def _check(q, k, v, causal, dev, kv_len=None, tol=TOL):
+    from b200k import fmha
+    o = fmha.fmha_fwd(q.to(dev), k.to(dev), v.to(dev), causal=causal, kv_len=kv_len)
+    torch.cuda.synchronize()
+    ref = oracle.fmha_ref(q, k, v, causal=causal, kv_lens=kv_len)
+    err = oracle.max_abs(o, ref)
+    assert err <= tol, err
+    assert not torch.isnan(o).any()
+    return o
+
+
+def test_uniform_v_and_onehot(cuda_device):
+    """Structured inputs that pin operand layouts exactly: with V constant along keys
+    the output equals that constant row; with one very large logit per query the
+    output equals the selected V row."""
+    from b200k import fmha, inputs
+    B, H, S, D = 1, 2, 256, 128
+    q, k, v = inputs.fmha_inputs(B, H, H, S, S, D, torch.float16, seed=7)
+    vconst = torch.arange(D, dtype=torch.float16).view(1, 1, 1, D).expand(B, H, S, D).contiguous() / 16
+    o = fmha.fmha_fwd(q.to(cuda_device), k.to(cuda_device), vconst.to(cuda_device))
+    assert torch.allclose(o.cpu().float(), vconst.float(), atol=2e-2)
+    # q_i = 12 * e_{i mod D}, k_j = 12 * e_{perm[j] mod D} on the first D keys, others 0
+    q = torch.zeros(B, H, S, D, dtype=torch.float16)
+    k = torch.zeros(B, H, S, D, dtype=torch.float16)
+    g = torch.Generator().manual_seed(3)
+    perm = torch.randperm(D, generator=g)
+    for i in range(S):
+        q[..., i, i % D] = 12.0
+    for j in range(D):
+        k[..., j, perm[j]] = 12.0
+    o = fmha.fmha_fwd(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), scale=1.0).cpu()
+    ref = oracle.fmha_ref(q, k, v, scale=1.0)
+    assert oracle.max_abs(o, ref) <= 4e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("S", [128, 256, 384, 1024])
+def test_parity_square(cuda_device, S, D, causal, dtype):
+    from b200k import inputs
+    q, k, v = inputs.fmha_inputs(2, 4, 4, S, S, D, dtype, seed=S + D)
+    _check(q, k, v, causal, cuda_device, tol=TOL if dtype == torch.float16 else 8e-3)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("S", [1, 17, 64, 65, 129, 257, 300, 513])
+def test_parity_ragged(cuda_device, S, causal):
+    """Sequence lengths that are not multiples of the tile (the reference pads to 64 in
+    Python; here the kernel clips)."""
+    from b200k import inputs
+    q, k, v = inputs.fmha_inputs(1, 4, 4, S, S, 128, torch.float16, seed=S)
+    _check(q, k, v, causal, cuda_device)
+
+
+@pytest.mark.parametrize("group", [1, 4, 8])
+def test_parity_gqa(cuda_device, group):
+    from b200k import inputs
+    q, k, v = inputs.fmha_inputs(2, 8, 8 // group, 384, 384, 128, torch.float16, seed=group)
+    _check(q, k, v, True, cuda_device)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_parity_cross_lengths(cuda_device, causal):
+    """Sq != Skv (bottom-right aligned diagonal) and a valid length below Skv with NaN
+    in the padding: padded keys must never reach the result."""
+    from b200k import inputs
+    q, k, v = inputs.fmha_inputs(1, 4, 2, 200, 700, 128, torch.float16, seed=9)
+    _check(q, k, v, causal, cuda_device)
+    k[:, :, 555:] = float("nan")
+    v[:, :, 555:] = float("nan")
+    _check(q, k, v, causal, cuda_device, kv_len=555)
+    # more queries than keys: the first rows see no key at all under the causal rule -> zeros
+    q2, k2, v2 = inputs.fmha_inputs(1, 2, 2, 300, 100, 128, torch.float16, seed=10)
+    _check(q2, k2, v2, causal, cuda_device)
+
+
+def test_bshd_storage_is_zero_copy(cuda_device):
+    """Tensors stored [B,S,H,D] and viewed [B,H,S,D] are consumed through strides."""
+    from b200k import fmha, inputs
+    q, k, v = inputs.fmha_inputs(2, 8, 2, 320, 320, 128, torch.float16, seed=12)
+    qs, ks, vs = inputs.fmha_inputs(2, 8, 2, 320, 320, 128, torch.float16, device=cuda_device, seed=12, layout="bshd")
+    assert not qs.is_contiguous()
+    out = torch.empty(2, 320, 8, 128, dtype=torch.float16, device=cuda_device).transpose(1, 2)
+    fmha.fmha_fwd(qs, ks, vs, causal=True, out=out)
+    assert oracle.max_abs(out, oracle.fmha_ref(q, k, v, causal=True)) <= TOL
+
+
+def test_config3_sample_heads(cuda_device):
+    """Causal fp16 B=1, 32/8 heads, s=4096, d=128 from seed 2: CPU check of the first and
+    last query head of two KV groups (all 4096 rows each), through fine_fmha."""
+    from b200k import inputs
+    import fmha_unified
+    q, k, v = inputs.fmha_c3()
+    o = fmha_unified.ops.fine_fmha(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), True, False, 5)
+    assert o.shape == q.shape and o.dtype == q.dtype
+    for h in (0, 3, 28, 31):
+        ref = oracle.fmha_ref(q[:, h:h + 1], k[:, h // 4:h // 4 + 1], v[:, h // 4:h // 4 + 1], causal=True)
+        err = oracle.max_abs(o[:, h:h + 1], ref)
+        assert err <= TOL, (h, err)
+
+
+@pytest.mark.parametrize("D,S,causal", [(64, 1024, True), (128, 2048, False), (128, 2048, True)])
+def test_config4_bf16_sample(cuda_device, D, S, causal):
+    """bf16 MHA prefill shapes (B=8, 32 heads): one (batch, head) pair per corner on the CPU."""
+    from b200k import fmha, inputs
+    q, k, v = inputs.fmha_inputs(8, 32, 32, S, S, D, torch.bfloat16, device=cuda_device, seed=3)
+    o = fmha.fmha_fwd(q, k, v, causal=causal)
+    for (b, h) in ((0, 0), (7, 31), (3, 17)):
+        ref = oracle.fmha_ref(q[b:b + 1, h:h + 1].cpu(), k[b:b + 1, h:h + 1].cpu(), v[b:b + 1, h:h + 1].cpu(),
+                              causal=causal)
+        err = oracle.max_abs(o[b:b + 1, h:h + 1], ref)
+        assert err <= 8e-3, (b, h, err)  # bf16 output rounding: 2^-9 relative on |o| <~ 2
+
+
+def test_determinism_and_batch_independence(cuda_device):
+    """Same launch three times is bit-identical; a (batch, head) shard computed alone equals
+    the same slice of the full launch bit for bit (the sharding used across GPUs)."""
+    from b200k import fmha, inputs
+    q, k, v = inputs.fmha_inputs(4, 8, 2, 512, 512, 128, torch.float16, device=cuda_device, seed=21)
+    outs = [fmha.fmha_fwd(q, k, v, causal=True) for _ in range(3)]
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    part = fmha.fmha_fwd(q[1:3, 4:8], k[1:3, 1:2], v[1:3, 1:2], causal=True)
+    assert torch.equal(part, outs[0][1:3, 4:8])
+
+
+def test_reference_wrapper_semantics(cuda_device):
+    """fine_fmha keeps the reference's signature, shapes and error behaviour."""
+    import fmha_unified
+    from b200k import inputs
+    q, k, v = inputs.fmha_inputs(1, 4, 1, 100, 100, 128, torch.float16, device=cuda_device, seed=4)
+    for idx in range(6):
+        o = fmha_unified.ops.fine_fmha(q, k, v, True, False, idx)
+        assert o.shape == (1, 4, 100, 128)
+    ref = oracle.fmha_ref(q, k, v, causal=True)
+    assert oracle.max_abs(o, ref) <= TOL
+    with pytest.raises(RuntimeError):
+        fmha_unified.ops.fine_fmha(q, k, v, True, True, 0)       # causal together with decode
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        fmha_unified.ops.fine_fmha(q, k, v, True, False, 6)      # declared, not implemented
+    with pytest.raises(RuntimeError):
+        fmha_unified.ops.fine_fmha(q.float(), k.float(), v.float(), True, False, 0)

@@ -1,0 +1,104 @@
+"""Tensor-level wrappers of b200k_fmha_fwd and b200k_fmha_decode_splitkv."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+
+
+def _check_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
+    # conditions of the reference launchers
+    # (kernels/fmha/pkg/fmha_unified/csrc/semi/fmha_4_nv.cu:397-417), plus bf16 and d = 64
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise RuntimeError("q, k, v must be [batch, heads, seq, head_dim]")
+    if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise RuntimeError(f"q, k, v must all be float16 or bfloat16, got {q.dtype}, {k.dtype}, {v.dtype}")
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise RuntimeError("q, k, v must be CUDA tensors")
+    if not (q.device == k.device == v.device):
+        raise RuntimeError("q, k, v must be on the same device")
+    B, Hq, Sq, D = q.shape
+    if k.shape != v.shape or k.size(0) != B or k.size(3) != D:
+        raise RuntimeError(f"shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}")
+    if k.size(1) == 0 or Hq % k.size(1) != 0:
+        raise RuntimeError("number of query heads must be a multiple of the number of KV heads")
+    if D not in (64, 128):
+        raise RuntimeError(f"head_dim must be 64 or 128, got {D}")
+
+
+def _rows_contiguous(t: torch.Tensor) -> torch.Tensor:
+    """The kernels need the head_dim axis contiguous and 16-byte aligned strides;
+    anything else (rare) is copied once."""
+    if t.stride(3) != 1 or any(s % 8 for s in t.stride()[:3]) or t.data_ptr() % 16:
+        return t.contiguous()
+    return t
+
+
+def fmha_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = False, kv_len: int | None = None,
+             scale: float | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """softmax(q k^T scale + mask) v; q [B,Hq,Sq,D], k, v [B,Hkv,Skv,D] (any batch/head/row strides)."""
+    _check_qkv(q, k, v)
+    B, Hq, Sq, D = q.shape
+    Hkv, Skv = k.size(1), k.size(2)
+    if kv_len is None:
+        kv_len = Skv
+    if out is None:
+        out = torch.empty((B, Hq, Sq, D), dtype=q.dtype, device=q.device)
+    if Sq == 0 or B == 0:
+        return out
+    if Skv == 0 or kv_len <= 0:
+        return out.zero_()
+    q, k, v = _rows_contiguous(q), _rows_contiguous(k), _rows_contiguous(v)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    L = _lib.lib()
+    with torch.cuda.device(q.device):
+        code = L.b200k_fmha_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, Hq, Hkv, Sq, Skv, D,
+                                _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(out),
+                                float(scale), int(bool(causal)), int(min(kv_len, Skv)), _DTYPES[q.dtype], 0,
+                                torch.cuda.current_stream(q.device).cuda_stream)
+    _lib.check(code, "b200k_fmha_fwd")
+    return out
+
+
+def decode_workspace(B: int, Hq: int, Hkv: int, Sq: int, Skv: int, D: int, num_splits: int, device) -> torch.Tensor:
+    n = _lib.lib().b200k_fmha_decode_workspace_bytes(B, Hq, Hkv, Sq, Skv, D, num_splits)
+    return torch.empty(max(int(n), 16), dtype=torch.uint8, device=device)
+
+
+def fmha_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_lens: torch.Tensor | None = None,
+                num_splits: int = 0, scale: float | None = None, out: torch.Tensor | None = None,
+                workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """Split-KV attention for decode-shaped inputs (q [B,Hq,Sq,D] with small Sq, normally 1).
+    kv_lens: int32 [B] on the device (valid keys of each sequence) or None for all of Skv."""
+    _check_qkv(q, k, v)
+    B, Hq, Sq, D = q.shape
+    Hkv, Skv = k.size(1), k.size(2)
+    if out is None:
+        out = torch.empty((B, Hq, Sq, D), dtype=q.dtype, device=q.device)
+    if Sq == 0 or B == 0:
+        return out
+    if Skv == 0:
+        return out.zero_()
+    q, k, v = _rows_contiguous(q), _rows_contiguous(k), _rows_contiguous(v)
+    if kv_lens is not None:
+        if kv_lens.dtype != torch.int32 or kv_lens.device != q.device or kv_lens.numel() != B:
+            raise RuntimeError("kv_lens must be an int32 tensor with one entry per batch element on q's device")
+        kv_lens = kv_lens.contiguous()
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    L = _lib.lib()
+    with torch.cuda.device(q.device):
+        if workspace is None:
+            workspace = decode_workspace(B, Hq, Hkv, Sq, Skv, D, num_splits, q.device)
+        code = L.b200k_fmha_decode_splitkv(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, Hq, Hkv, Sq, Skv, D,
+            _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(out), float(scale),
+            kv_lens.data_ptr() if kv_lens is not None else None, int(num_splits), _DTYPES[q.dtype],
+            workspace.data_ptr(), workspace.numel(), torch.cuda.current_stream(q.device).cuda_stream)
+    _lib.check(code, "b200k_fmha_decode_splitkv")
+    return out

@@ -1,7 +1,494 @@
-// placeholder translation unit, replaced by the prefill kernel
+// Fused multi-head attention forward for sm_100a:
+//   O = softmax(Q K^T * scale + mask) V, online softmax in fp32, causal mask, GQA.
+//
+// One CTA owns two 128-row query tiles of one (batch, head) and walks the keys in
+// blocks of 128:
+//   warps 0-3   softmax group of tile 0 (thread = query row = TMEM lane)
+//   warps 4-7   softmax group of tile 1
+//   warp  8     TMA loader: Q tiles once, K and V blocks through 2-deep rings
+//   warp  9     MMA issuer: S_i = Q_i K_j^T (both operands K-major) into TMEM, then
+//               O_i += P_i V_j with P_i read from TMEM and V_j as an MN-major
+//               shared-memory operand (V is [kv, d] with d contiguous)
+// While one tile's softmax runs on the CUDA cores the tensor core works on the
+// other tile.  A softmax thread loads its whole S row with tcgen05.ld, takes the
+// row max, rescales O in TMEM only when the max grew by more than 2^8 (the
+// stale max is exact algebra: numerator and denominator carry the same factor),
+// writes P = exp2(s*scale*log2e - m) as 16-bit pairs over the S columns and adds
+// the row sum.  The epilogue scales O by 1/l, stages it in the (now free) Q tile
+// and stores it with TMA, which also clips the ragged last tile.
+//
+// Reference semantics: kernels/fmha/pkg/fmha_unified/csrc/semi/fmha_2_nv.cu
+// (:36-48 GQA + offsets, :93-97 causal block range, :177-185 mask + scale,
+// :188-208 recurrences, :283 final O/l) and manual/fmha_5_nv.cu:25-133.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math.h>
+
 #include "host_common.h"
-extern "C" int b200k_fmha_fwd(const void*, const void*, const void*, void*, int, int, int, int, int, int,
-                              const int64_t*, const int64_t*, const int64_t*, const int64_t*, float, int, int, int,
-                              int, b200k_stream_t) {
-  return B200K_EARG;
+#include "ptx.cuh"
+
+namespace b200k {
+namespace {
+
+constexpr int kFmhaThreads = 320;
+constexpr int kTile = 128;  // query rows per tile and keys per block
+constexpr float kRescaleThreshold = 8.0f;
+
+template <int D>
+struct FmhaSmem {
+  static constexpr uint32_t kTileBytes = kTile * D * 2;  // one Q tile, K block or V block
+  static constexpr uint32_t kHalfBytes = kTile * 128;    // one 64-wide (128-byte) column box
+  static constexpr uint32_t kQOff = 0;
+  static constexpr uint32_t kKOff = 2 * kTileBytes;
+  static constexpr uint32_t kVOff = 4 * kTileBytes;
+  static constexpr uint32_t kBarOff = 6 * kTileBytes;
+  static constexpr uint32_t kTotal = kBarOff + 256 + 1024;
+};
+
+struct FmhaParams {
+  int B, Hq, Hkv, Sq;
+  int kv_len;      // valid keys (<= Skv); the K/V tensor maps end there
+  int causal;
+  int num_pairs;   // ceil(Sq / 256)
+  float scale_log2;
+  int* status;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  if constexpr (BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kFmhaThreads, 1)
+fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                const FmhaParams p) {
+  using L = FmhaSmem<D>;
+  constexpr int kDBoxes = D / 64;  // 64-wide column boxes per row
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kSCol0 = 0, kSCol1 = 128, kOCol0 = 256, kOCol1 = 256 + D;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* q_full = bars;        // [2]
+  uint64_t* k_full = bars + 2;    // [2]
+  uint64_t* k_empty = bars + 4;   // [2]
+  uint64_t* v_full = bars + 6;    // [2]
+  uint64_t* v_empty = bars + 8;   // [2]
+  uint64_t* s_full = bars + 10;   // [2]
+  uint64_t* p_ready = bars + 12;  // [2]
+  uint64_t* o_full = bars + 14;   // [2]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 16);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- which work item ----
+  const int idx = blockIdx.x;
+  const int h = idx % p.Hq;
+  const int t = idx / p.Hq;
+  const int b = t % p.B;
+  const int pair = p.num_pairs - 1 - t / p.B;  // heavy (late) causal tiles first
+  const int hk = h / (p.Hq / p.Hkv);
+  const int off = p.kv_len - p.Sq;  // causal diagonal, aligned bottom-right
+  int q0[2], nb[2];
+  bool valid[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    q0[i] = (pair * 2 + i) * kTile;
+    valid[i] = q0[i] < p.Sq;
+    int kv_hi = p.kv_len;
+    if (p.causal) {
+      const int last_row = min(q0[i] + kTile, p.Sq) - 1;
+      kv_hi = max(0, min(p.kv_len, last_row + off + 1));
+    }
+    nb[i] = valid[i] ? (kv_hi + kTile - 1) / kTile : 0;
+  }
+  const int nb_max = max(nb[0], nb[1]);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_ready[i], 128);
+      mbar_init(&o_full[i], 1);
+    }
+    fence_mbar_init();
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+    prefetch_tmap(&tmO);
+  }
+  if (warp == 9) {
+    tmem_alloc<1>(tmem_holder, kTmemCols);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 8) {
+    // ------------------------------- TMA loader -------------------------------
+    if (elect_one() && nb_max > 0) {
+      auto load_tile = [&](const CUtensorMap* tm, uint8_t* dst, uint64_t* bar, int row, int head) {
+        mbar_expect_tx(bar, L::kTileBytes);
+#pragma unroll
+        for (int d = 0; d < kDBoxes; ++d) tma_load_4d(dst + d * L::kHalfBytes, tm, bar, d * 64, row, head, b);
+      };
+      bool ok = true;
+      load_tile(&tmK, smem + L::kKOff, &k_full[0], 0, hk);
+      for (int i = 0; i < 2; ++i)
+        if (nb[i] > 0) load_tile(&tmQ, smem + L::kQOff + i * L::kTileBytes, &q_full[i], q0[i], h);
+      for (int j = 0; j < nb_max && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&v_empty[s], ph ^ 1)) {
+          report_timeout(p.status, KID_FMHA, ROLE_PRODUCER);
+          break;
+        }
+        load_tile(&tmV, smem + L::kVOff + s * L::kTileBytes, &v_full[s], j * kTile, hk);
+        if (j + 1 < nb_max) {
+          const int s1 = (j + 1) & 1;
+          const uint32_t ph1 = ((j + 1) >> 1) & 1;
+          if (!mbar_wait(&k_empty[s1], ph1 ^ 1)) {
+            report_timeout(p.status, KID_FMHA, ROLE_PRODUCER);
+            break;
+          }
+          load_tile(&tmK, smem + L::kKOff + s1 * L::kTileBytes, &k_full[s1], (j + 1) * kTile, hk);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (elect_one() && nb_max > 0) {
+      constexpr uint32_t idesc_s = make_idesc_f16(BF16 ? 1 : 0, 0, 0, kTile, kTile);
+      constexpr uint32_t idesc_pv = make_idesc_f16(BF16 ? 1 : 0, 0, 1, kTile, D);
+      const uint32_t q_addr = smem_u32(smem + L::kQOff);
+      const uint32_t k_addr = smem_u32(smem + L::kKOff);
+      const uint32_t v_addr = smem_u32(smem + L::kVOff);
+      const uint32_t s_col[2] = {kSCol0, kSCol1};
+      const uint32_t o_col[2] = {kOCol0, kOCol1};
+      bool ok = true;
+      auto fail = [&]() {
+        report_timeout(p.status, KID_FMHA, ROLE_MMA);
+        ok = false;
+      };
+      // S_i = Q_i . K_stage^T : D/16 steps; 16 d-elements = 32 bytes inside a 128-byte row,
+      // the next 64-wide column box is kHalfBytes further.
+      auto issue_s = [&](int i, int stage) {
+        const uint32_t qa = q_addr + i * L::kTileBytes;
+        const uint32_t ka = k_addr + stage * L::kTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t o = (kk >> 2) * L::kHalfBytes + (kk & 3) * 32;
+          umma_ss<1>(tmem_base + s_col[i], make_smem_desc_sw128(qa + o, 16, 1024),
+                     make_smem_desc_sw128(ka + o, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit<1>(&s_full[i]);
+      };
+      // O_i += P_i . V_stage : 8 steps of 16 keys; P from TMEM (8 columns of 16-bit pairs per
+      // step), V MN-major: 16 keys = 16 rows of 128 bytes; 64-wide d boxes kHalfBytes apart.
+      auto issue_pv = [&](int i, int stage, bool first) {
+        const uint32_t va = v_addr + stage * L::kTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk) {
+          umma_ts(tmem_base + o_col[i], tmem_base + s_col[i] + kk * 8,
+                  make_smem_desc_sw128(va + kk * 2048, L::kHalfBytes, 1024), idesc_pv,
+                  (!first || kk > 0) ? 1u : 0u);
+        }
+      };
+      if (!mbar_wait(&k_full[0], 0)) fail();
+      for (int i = 0; i < 2 && ok; ++i) {
+        if (nb[i] > 0) {
+          if (!mbar_wait(&q_full[i], 0)) {
+            fail();
+            break;
+          }
+          tc_fence_after();
+          issue_s(i, 0);
+        }
+      }
+      if (ok) umma_commit<1>(&k_empty[0]);
+      for (int j = 0; j < nb_max && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&v_full[s], ph)) {
+          fail();
+          break;
+        }
+        bool k_next_ready = false;
+        for (int i = 0; i < 2 && ok; ++i) {
+          if (j >= nb[i]) continue;
+          if (!mbar_wait(&p_ready[i], j & 1)) {
+            fail();
+            break;
+          }
+          tc_fence_after();
+          issue_pv(i, s, j == 0);
+          if (j == nb[i] - 1) umma_commit<1>(&o_full[i]);
+          if (j + 1 < nb[i]) {
+            const int s1 = (j + 1) & 1;
+            if (!k_next_ready) {
+              if (!mbar_wait(&k_full[s1], ((j + 1) >> 1) & 1)) {
+                fail();
+                break;
+              }
+              tc_fence_after();
+              k_next_ready = true;
+            }
+            issue_s(i, s1);
+          }
+        }
+        if (!ok) break;
+        umma_commit<1>(&v_empty[s]);
+        if (j + 1 < nb_max) umma_commit<1>(&k_empty[(j + 1) & 1]);
+      }
+    }
+  } else {
+    // ----------------------------- softmax groups -----------------------------
+    const int i = warp >> 2;             // tile of this group
+    const int row = threadIdx.x & 127;   // query row inside the tile = TMEM lane
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t s_tmem = tmem_base + lane_sel + (i == 0 ? kSCol0 : kSCol1);
+    const uint32_t o_tmem = tmem_base + lane_sel + (i == 0 ? kOCol0 : kOCol1);
+    if (valid[i]) {
+      const float sc = p.scale_log2;
+      const int q = q0[i] + row;
+      // last visible key index for this row
+      const int lim_row = p.causal ? min(q + off, p.kv_len - 1) : p.kv_len - 1;
+      float m_use = -INFINITY;
+      float l = 0.f;
+      bool ok = true;
+      for (int j = 0; j < nb[i]; ++j) {
+        if (!mbar_wait(&s_full[i], j & 1)) {
+          if (lane == 0) report_timeout(p.status, KID_FMHA, ROLE_SOFTMAX);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint32_t s[128];
+        tmem_ld32(s_tmem + 0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        tmem_ld32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+        tmem_ld32(s_tmem + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
+        tmem_ld32(s_tmem + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
+        tmem_ld_wait();
+        const int k0 = j * kTile;
+        // does any row of this tile see a masked key in this block?
+        const int tile_min_lim = p.causal ? min(q0[i] + off, p.kv_len - 1) : p.kv_len - 1;
+        if (k0 + kTile - 1 > tile_min_lim) {
+          const int lim = lim_row - k0;  // keys with local index > lim are masked
+#pragma unroll
+          for (int k = 0; k < 128; ++k)
+            if (k > lim) s[k] = 0xff800000u;  // -inf
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < 128; k += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(s[k + 0]));
+          mx1 = fmaxf(mx1, __uint_as_float(s[k + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(s[k + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(s[k + 3]));
+        }
+        const float m_new = fmaxf(m_use, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc);
+        if (j == 0) {
+          m_use = m_new;
+        } else {
+          const bool need = (m_new - m_use) > kRescaleThreshold;
+          if (__any_sync(0xffffffffu, need)) {
+            const float f = (m_new == -INFINITY) ? 1.f : ex2(m_use - m_new);
+            m_use = m_new;
+            l *= f;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld32(o_tmem + c * 32, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
+              tmem_st32(o_tmem + c * 32, o);
+            }
+          }
+        }
+        const float neg = (m_use == -INFINITY) ? 0.f : -m_use;
+        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const int k = c * 64 + e * 2;
+            const float p0 = ex2(fmaf(__uint_as_float(s[k + 0]), sc, neg));
+            const float p1 = ex2(fmaf(__uint_as_float(s[k + 1]), sc, neg));
+            const float p2 = ex2(fmaf(__uint_as_float(s[k + 2]), sc, neg));
+            const float p3 = ex2(fmaf(__uint_as_float(s[k + 3]), sc, neg));
+            sum0 += p0;
+            sum1 += p1;
+            sum2 += p2;
+            sum3 += p3;
+            pk[e] = pack16<BF16>(p0, p1);
+            pk[e + 1] = pack16<BF16>(p2, p3);
+          }
+          tmem_st32(s_tmem + c * 32, pk);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&p_ready[i]);
+        l += (sum0 + sum1) + (sum2 + sum3);
+      }
+
+      // ------------------------------ epilogue ------------------------------
+      if (ok && nb[i] > 0) {
+        if (!mbar_wait(&o_full[i], 0)) {
+          if (lane == 0) report_timeout(p.status, KID_FMHA, ROLE_EPILOGUE);
+          ok = false;
+        }
+        tc_fence_after();
+      }
+      if (ok) {
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        uint8_t* stage = smem + L::kQOff + i * L::kTileBytes;  // Q_i is no longer read
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          if (nb[i] > 0) {
+            tmem_ld32(o_tmem + c * 32, o);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = 0u;
+          }
+          uint8_t* rowp = stage + (c >> 1) * L::kHalfBytes + row * 128;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 w;
+            w.x = pack16<BF16>(__uint_as_float(o[8 * g + 0]) * inv, __uint_as_float(o[8 * g + 1]) * inv);
+            w.y = pack16<BF16>(__uint_as_float(o[8 * g + 2]) * inv, __uint_as_float(o[8 * g + 3]) * inv);
+            w.z = pack16<BF16>(__uint_as_float(o[8 * g + 4]) * inv, __uint_as_float(o[8 * g + 5]) * inv);
+            w.w = pack16<BF16>(__uint_as_float(o[8 * g + 6]) * inv, __uint_as_float(o[8 * g + 7]) * inv);
+            const int chunk = (c & 1) * 4 + g;
+            *reinterpret_cast<uint4*>(rowp + ((chunk ^ (row & 7)) << 4)) = w;
+          }
+        }
+        fence_proxy_async_smem();
+        named_barrier_sync(1 + i, 128);
+        if (row == 0) {
+#pragma unroll
+          for (int d = 0; d < kDBoxes; ++d) tma_store_4d(&tmO, stage + d * L::kHalfBytes, d * 64, q0[i], h, b);
+          tma_store_commit();
+          tma_store_wait_all<0>();
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, kTmemCols);
+  }
+}
+
+int make_map_bhsd(CUtensorMap* tm, const void* base, int D, int S, int H, int B, const int64_t st[3]) {
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)S, (uint64_t)H, (uint64_t)B};
+  uint64_t strides[3] = {(uint64_t)st[2] * 2, (uint64_t)st[1] * 2, (uint64_t)st[0] * 2};
+  uint32_t box[4] = {64, (uint32_t)kTile, 1, 1};
+  return encode_tmap_16bit(tm, base, 4, dims, strides, box, true);
+}
+
+template <int D, bool BF16>
+int launch_fmha(const void* Q, const void* K, const void* V, void* O, int B, int Hq, int Hkv, int Sq, int kv_len,
+                const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, float scale, int causal,
+                cudaStream_t stream) {
+  using L = FmhaSmem<D>;
+  auto kfn = fmha_fwd_kernel<D, BF16>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev & 63]) {
+    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return B200K_ECUDA;
+    }
+    configured[dev & 63] = true;
+  }
+  CUtensorMap tmQ, tmK, tmV, tmO;
+  int r;
+  if ((r = make_map_bhsd(&tmQ, Q, D, Sq, Hq, B, qs))) return r;
+  if ((r = make_map_bhsd(&tmK, K, D, kv_len, Hkv, B, ks))) return r;
+  if ((r = make_map_bhsd(&tmV, V, D, kv_len, Hkv, B, vs))) return r;
+  if ((r = make_map_bhsd(&tmO, O, D, Sq, Hq, B, os))) return r;
+  FmhaParams p;
+  p.B = B;
+  p.Hq = Hq;
+  p.Hkv = Hkv;
+  p.Sq = Sq;
+  p.kv_len = kv_len;
+  p.causal = causal;
+  p.num_pairs = (Sq + 2 * kTile - 1) / (2 * kTile);
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status_ptr();
+  if (!p.status) return B200K_ECUDA;
+  const long grid = (long)p.num_pairs * Hq * B;
+  if (grid <= 0 || grid > 0x7fffffffL) return B200K_ESHAPE;
+  kfn<<<(unsigned)grid, kFmhaThreads, L::kTotal, stream>>>(tmQ, tmK, tmV, tmO, p);
+  count_launch();
+  return check_launch();
+}
+
+bool strides_ok(const void* ptr, const int64_t* st) {
+  return aligned16(ptr) && st[0] % 8 == 0 && st[1] % 8 == 0 && st[2] % 8 == 0 && st[0] >= 0 && st[1] >= 0 &&
+         st[2] > 0;
+}
+
+}  // namespace
+}  // namespace b200k
+
+using namespace b200k;
+
+extern "C" int b200k_fmha_fwd(const void* Q, const void* K, const void* V, void* O, int B, int Hq, int Hkv, int Sq,
+                              int Skv, int D, const int64_t q_strides[3], const int64_t k_strides[3],
+                              const int64_t v_strides[3], const int64_t o_strides[3], float scale, int causal,
+                              int kv_len, int dtype, int variant, b200k_stream_t stream_) {
+  (void)variant;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (dtype != B200K_F16 && dtype != B200K_BF16) return B200K_EDTYPE;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0 || Hq % Hkv != 0) return B200K_ESHAPE;
+  if (D != 64 && D != 128) return B200K_EHEADDIM;
+  if (!Q || !K || !V || !O || !q_strides || !k_strides || !v_strides || !o_strides) return B200K_EARG;
+  if (kv_len <= 0 || kv_len > Skv) return B200K_EARG;
+  if (!(scale > 0.f)) return B200K_EARG;
+  if (!strides_ok(Q, q_strides) || !strides_ok(K, k_strides) || !strides_ok(V, v_strides) ||
+      !strides_ok(O, o_strides))
+    return B200K_EALIGN;
+  if (!b200k_device_supported()) return B200K_ENOGPU;
+  const bool bf16 = dtype == B200K_BF16;
+  if (D == 128)
+    return bf16 ? launch_fmha<128, true>(Q, K, V, O, B, Hq, Hkv, Sq, kv_len, q_strides, k_strides, v_strides,
+                                         o_strides, scale, causal, stream)
+                : launch_fmha<128, false>(Q, K, V, O, B, Hq, Hkv, Sq, kv_len, q_strides, k_strides, v_strides,
+                                          o_strides, scale, causal, stream);
+  return bf16 ? launch_fmha<64, true>(Q, K, V, O, B, Hq, Hkv, Sq, kv_len, q_strides, k_strides, v_strides, o_strides,
+                                      scale, causal, stream)
+              : launch_fmha<64, false>(Q, K, V, O, B, Hq, Hkv, Sq, kv_len, q_strides, k_strides, v_strides,
+                                       o_strides, scale, causal, stream);
 }
