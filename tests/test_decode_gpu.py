@@ -1,0 +1,118 @@
+"""GPU parity of the split-KV decode path against the CPU oracle, through the C ABI
+(b200k_fmha_decode_splitkv via ctypes) and the reference-facing ops.
+Tolerance: max-abs <= 2e-3 against fp32 softmax(QK^T scale)V (the stated bar)."""
+import pytest
+import torch
+
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL = oracle.FMHA_MAX_ABS_TOL
+
+
+def _decode(q, k, v, lens, dev, **kw):
+    from b200k import fmha
+    o = fmha.fmha_decode(q.to(dev), k.to(dev), v.to(dev),
+                         kv_lens=None if lens is None else lens.to(dev), **kw)
+    torch.cuda.synchronize()
+    return o.cpu()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("Skv", [1, 15, 64, 65, 200, 1000, 4096])
+def test_parity_uniform_length(cuda_device, Skv, D, dtype):
+    from b200k import inputs
+    q, k, v = inputs.fmha_inputs(3, 8, 2, 1, Skv, D, dtype, seed=Skv + D)
+    o = _decode(q, k, v, None, cuda_device)
+    ref = oracle.fmha_ref(q, k, v)
+    err = oracle.max_abs(o, ref)
+    # bf16 keeps 8 significant bits: output and P rounding cost up to 2^-8 max|o| on top
+    assert err <= (TOL if dtype == torch.float16 else TOL + float(ref.abs().max()) * 2.0 ** -8), err
+
+
+@pytest.mark.parametrize("splits", [0, 1, 2, 7, 32])
+def test_parity_varlen_nan_padding(cuda_device, splits):
+    """Per-sequence lengths over a padded batch; the padding holds NaN, which must never
+    reach the result; every split count gives the same answer within tolerance."""
+    from b200k import inputs
+    B, Hq, Hkv, Skv, D = 6, 32, 8, 2048, 128
+    q, k, v = inputs.fmha_inputs(B, Hq, Hkv, 1, Skv, D, torch.float16, seed=4)
+    lens = torch.tensor([1, 63, 64, 700, 2047, 2048], dtype=torch.int32)
+    for b in range(B):
+        k[b, :, int(lens[b]):] = float("nan")
+        v[b, :, int(lens[b]):] = float("nan")
+    o = _decode(q, k, v, lens, cuda_device, num_splits=splits)
+    assert not torch.isnan(o).any()
+    err = oracle.max_abs(o, oracle.fmha_ref(q, k, v, kv_lens=lens))
+    assert err <= TOL, err
+
+
+@pytest.mark.parametrize("Hq,Hkv,Sq", [(8, 8, 1), (8, 1, 1), (16, 1, 1), (4, 2, 4), (8, 2, 3)])
+def test_parity_row_groups(cuda_device, Hq, Hkv, Sq):
+    """GQA ratios 1, 8, 16 and several query rows per sequence (all rows see every key)."""
+    from b200k import inputs
+    q, k, v = inputs.fmha_inputs(2, Hq, Hkv, Sq, 777, 128, torch.float16, seed=Hq * 10 + Sq)
+    o = _decode(q, k, v, None, cuda_device)
+    assert oracle.max_abs(o, oracle.fmha_ref(q, k, v)) <= TOL
+
+
+def test_zero_length_sequence_gives_zeros(cuda_device):
+    from b200k import inputs
+    q, k, v = inputs.fmha_inputs(2, 8, 2, 1, 256, 128, torch.float16, seed=8)
+    lens = torch.tensor([0, 100], dtype=torch.int32)
+    o = _decode(q, k, v, lens, cuda_device)
+    assert torch.count_nonzero(o[0]) == 0
+    assert oracle.max_abs(o[1:], oracle.fmha_ref(q[1:], k[1:], v[1:], kv_lens=lens[1:])) <= TOL
+
+
+def test_config5_shape_reduced_batch(cuda_device):
+    """The decode configuration (fp16, 32 query / 8 KV heads, d=128, lengths uniform in
+    [512, 32768], padded batch) with 8 of its 64 sequences checked on the CPU, through the
+    reference-facing varlen op; plus determinism (bit-identical reruns)."""
+    from b200k import inputs
+    import fmha_unified
+    B, Hq, Hkv, Skv, D = 8, 32, 8, 32768, 128
+    lens = inputs.decode_lens(64)[:B].clone()
+    lens[0], lens[1] = 512, 32768  # make sure both extremes are present
+    q = inputs.randn16((B, Hq, 1, D), 40, dtype=torch.float16)
+    k = inputs.device_randn16((B, Hkv, Skv, D), 41, dtype=torch.float16, device=cuda_device)
+    v = inputs.device_randn16((B, Hkv, Skv, D), 42, dtype=torch.float16, device=cuda_device)
+    dl = lens.to(cuda_device)
+    o1 = fmha_unified.ops.fine_fmha_decode_varlen(q.to(cuda_device), k, v, dl)
+    o2 = fmha_unified.ops.fine_fmha_decode_varlen(q.to(cuda_device), k, v, dl)
+    assert torch.equal(o1, o2)
+    ref = oracle.fmha_ref(q, k.cpu(), v.cpu(), kv_lens=lens)
+    assert oracle.max_abs(o1, ref) <= TOL
+
+
+def test_reference_signature_decode(cuda_device):
+    """fine_fmha(..., causal=False, is_decode=True, idx): the reference's decode call
+    (benchmarks/flashattn-cuda/modeling_llama.py:687-688) with a single query row."""
+    import fmha_unified
+    from b200k import inputs
+    q, k, v = inputs.fmha_inputs(2, 32, 8, 1, 900, 128, torch.float16, device=cuda_device, seed=6)
+    o = fmha_unified.ops.fine_fmha(q, k, v, False, True, 5)
+    assert o.shape == (2, 32, 1, 128)
+    assert oracle.max_abs(o, oracle.fmha_ref(q, k, v)) <= TOL
+
+
+def test_matches_prefill_kernel(cuda_device):
+    """The split-KV path and the tcgen05 prefill path agree on the same decode input."""
+    from b200k import fmha, inputs
+    q, k, v = inputs.fmha_inputs(4, 32, 8, 1, 3000, 128, torch.float16, device=cuda_device, seed=13)
+    a = fmha.fmha_decode(q, k, v)
+    b = fmha.fmha_fwd(q, k, v, causal=False)
+    assert float((a.float() - b.float()).abs().max()) <= TOL
+
+
+def test_workspace_errors(cuda_device):
+    from b200k import _lib, fmha, inputs
+    q, k, v = inputs.fmha_inputs(1, 8, 2, 1, 512, 128, torch.float16, device=cuda_device, seed=2)
+    small = torch.empty(16, dtype=torch.uint8, device=cuda_device)
+    with pytest.raises(_lib.B200KError) as e:
+        fmha.fmha_decode(q, k, v, num_splits=4, workspace=small)
+    assert e.value.code == -5
+    with pytest.raises(_lib.B200KError):  # 32 rows per KV head do not fit the 16-row tile
+        fmha.fmha_decode(*inputs.fmha_inputs(1, 32, 1, 1, 128, 128, torch.float16, device=cuda_device))

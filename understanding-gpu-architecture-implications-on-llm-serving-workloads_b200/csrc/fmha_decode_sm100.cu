@@ -1,9 +1,510 @@
-// placeholder translation unit, replaced by the split-KV decode kernels
+// Split-KV attention for decode-shaped inputs (few query rows per sequence).
+//
+// The workload is bound by HBM: every K and V element is read once and used by the
+// (Hq/Hkv * Sq <= 16) query rows that share its KV head, about 4 flop per byte.  So the
+// design variable is bytes in flight, not MMA shape:
+//   * grid (split, kv head, batch): CTA (s, hk, b) owns keys [s*chunk, (s+1)*chunk) of
+//     sequence b, clipped to its valid length kv_lens[b]; CTAs past the length exit.
+//   * warp 4 streams 64-key K and V tiles with TMA into a 4-deep ring (128 KB in flight
+//     per SM); warps 0-3 each consume a 16-key slice of every tile with ldmatrix +
+//     mma.sync m16n8k16 (the query rows padded to the 16-row MMA shape; the tensor-core
+//     rate is irrelevant here) and keep their own online-softmax state in registers,
+//     row statistics reduced across the 4 lanes of a quad with shuffles.
+//   * the 4 warps' states are merged through shared memory in a fixed order and written
+//     as one (max, sum, partial O) triple per (row, split) to the fp32 workspace;
+//   * a second kernel merges the splits of each row in a fixed order and writes 16-bit O.
+// Results are therefore bit-identical from run to run.
+//
+// Reference semantics: is_decode = true of
+// kernels/fmha/pkg/fmha_unified/csrc/semi/fmha_4_nv.cu:240-243,415-417 (non-causal, keys
+// beyond the length masked), GQA mapping of semi/fmha_2_nv.cu:36,42-45.  The reference
+// pads the single query row to 64 rows (kernels/fmha/pkg/fmha_unified/ops.py:19-25) and
+// has no split over keys.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math.h>
+
 #include "host_common.h"
-extern "C" int b200k_fmha_decode_splitkv(const void*, const void*, const void*, void*, int, int, int, int, int, int,
-                                         const int64_t*, const int64_t*, const int64_t*, const int64_t*, float,
-                                         const int32_t*, int, int, void*, size_t, b200k_stream_t) {
-  return B200K_EARG;
+#include "ptx.cuh"
+
+namespace b200k {
+namespace {
+
+constexpr int kDecThreads = 160;  // 4 consumer warps + 1 TMA warp
+constexpr int kDecTile = 64;      // keys per stage
+constexpr int kDecStages = 4;
+constexpr int kMaxRows = 16;
+
+template <int D>
+struct DecSmem {
+  static constexpr uint32_t kHalfBytes = kDecTile * 128;          // one 64-wide column box
+  static constexpr uint32_t kTileBytes = kDecTile * D * 2;        // K or V tile
+  static constexpr uint32_t kStageBytes = 2 * kTileBytes;         // K + V
+  static constexpr uint32_t kMergeOff = kDecStages * kStageBytes;  // fp32 [4 warps][16 rows][D]
+  static constexpr uint32_t kMergeBytes = 4 * kMaxRows * D * 4;
+  static constexpr uint32_t kMlOff = kMergeOff + kMergeBytes;      // fp32 [4 warps][16 rows][2]
+  static constexpr uint32_t kBarOff = kMlOff + 4 * kMaxRows * 2 * 4;
+  static constexpr uint32_t kTotal = kBarOff + 128 + 1024;
+};
+
+struct DecParams {
+  const void* q;
+  int64_t q_strides[3];
+  const int32_t* kv_lens;
+  float* part_o;   // [B][Hkv][R][num_splits][D]
+  float* part_ml;  // [B][Hkv][R][num_splits][2]
+  int B, Hq, Hkv, Sq, Skv;
+  int rows;        // R = Hq/Hkv * Sq
+  int num_splits;
+  int chunk;       // keys per split (multiple of kDecTile)
+  float scale_log2;
+  int* status;
+};
+
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
-extern "C" size_t b200k_fmha_decode_workspace_bytes(int, int, int, int, int, int, int) { return 0; }
-extern "C" int b200k_fmha_decode_auto_splits(int, int, int) { return 1; }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                                  uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+template <bool BF16>
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (BF16)
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  else
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack_p(float lo, float hi) {
+  if constexpr (BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+// Shared by the kernels below: where row r of a KV head lives in q / o.
+__device__ __forceinline__ int64_t row_offset(int r, int hk, int b, int G, int Sq, const int64_t* st) {
+  const int head = hk * G + r / Sq;
+  const int s = r % Sq;
+  return (int64_t)b * st[0] + (int64_t)head * st[1] + (int64_t)s * st[2];
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kDecThreads, 1)
+decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                      const DecParams p) {
+  using L = DecSmem<D>;
+  constexpr int kDBoxes = D / 64;
+  constexpr int kDTiles = D / 8;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* empty_bar = full_bar + kDecStages;
+  float* merge_o = reinterpret_cast<float*>(smem + L::kMergeOff);
+  float* merge_ml = reinterpret_cast<float*>(smem + L::kMlOff);
+
+  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int len = p.kv_lens ? p.kv_lens[b] : p.Skv;
+  len = max(0, min(len, p.Skv));
+  const int k_begin = split * p.chunk;
+  if (k_begin >= len) return;  // nothing for this split (uniform for the CTA)
+  const int k_end = min(len, k_begin + p.chunk);
+  const int n_tiles = (k_end - k_begin + kDecTile - 1) / kDecTile;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kDecStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 4);
+    }
+    fence_mbar_init();
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+  }
+  __syncthreads();
+
+  const int G = p.Hq / p.Hkv;
+  if (warp == 4) {
+    // ------------------------------- TMA producer -------------------------------
+    if (elect_one()) {
+      uint32_t stage = 0, phase = 0;
+      for (int t = 0; t < n_tiles; ++t) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+          report_timeout(p.status, KID_DECODE, ROLE_PRODUCER);
+          break;
+        }
+        uint8_t* sk = smem + stage * L::kStageBytes;
+        uint8_t* sv = sk + L::kTileBytes;
+        mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+        const int key0 = k_begin + t * kDecTile;
+#pragma unroll
+        for (int d = 0; d < kDBoxes; ++d) tma_load_4d(sk + d * L::kHalfBytes, &tmK, &full_bar[stage], d * 64, key0, hk, b);
+#pragma unroll
+        for (int d = 0; d < kDBoxes; ++d) tma_load_4d(sv + d * L::kHalfBytes, &tmV, &full_bar[stage], d * 64, key0, hk, b);
+        if (++stage == kDecStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // -------------------------------- consumers ---------------------------------
+    const int qrow = lane >> 2;  // MMA row of c[0], c[1]; c[2], c[3] are row qrow + 8
+    const int qcol = (lane & 3) * 2;
+    // Q as the A operand: 8 k-steps of 16 d; rows >= R are zero.
+    uint32_t qa[D / 16][4];
+    {
+      const uint16_t* qbase = reinterpret_cast<const uint16_t*>(p.q);
+      const bool lo_ok = qrow < p.rows, hi_ok = qrow + 8 < p.rows;
+      const int64_t off_lo = lo_ok ? row_offset(qrow, hk, b, G, p.Sq, p.q_strides) : 0;
+      const int64_t off_hi = hi_ok ? row_offset(qrow + 8, hk, b, G, p.Sq, p.q_strides) : 0;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const int d0 = ks * 16 + qcol;
+        qa[ks][0] = lo_ok ? *reinterpret_cast<const uint32_t*>(qbase + off_lo + d0) : 0u;
+        qa[ks][1] = hi_ok ? *reinterpret_cast<const uint32_t*>(qbase + off_hi + d0) : 0u;
+        qa[ks][2] = lo_ok ? *reinterpret_cast<const uint32_t*>(qbase + off_lo + d0 + 8) : 0u;
+        qa[ks][3] = hi_ok ? *reinterpret_cast<const uint32_t*>(qbase + off_hi + d0 + 8) : 0u;
+      }
+    }
+    float o[kDTiles][4];
+#pragma unroll
+    for (int dt = 0; dt < kDTiles; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    const float sc = p.scale_log2;
+
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    // ldmatrix lane roles
+    const int mi = lane >> 3, mr = lane & 7;
+    for (int t = 0; t < n_tiles; ++t) {
+      if (!mbar_wait(&full_bar[stage], phase)) {
+        if (lane == 0) report_timeout(p.status, KID_DECODE, ROLE_MMA);
+        ok = false;
+        break;
+      }
+      const uint32_t sk = smem_u32(smem + stage * L::kStageBytes);
+      const uint32_t sv = sk + L::kTileBytes;
+      const int slice0 = warp * 16;                          // first key of my slice inside the tile
+      const int key0 = k_begin + t * kDecTile + slice0;      // its global index
+      const int n_valid = k_end - key0;                      // keys of my slice that exist (may be <= 0)
+      if (n_valid < 16) {
+        // Rows at or beyond the valid length may hold anything (padding of the batch, even
+        // NaN): zero them in V so that P = 0 times V stays 0; S is masked below.
+        uint8_t* vrow = smem + stage * L::kStageBytes + L::kTileBytes;
+#pragma unroll
+        for (int it = 0; it < (16 * D * 2 / 16) / 32; ++it) {
+          const int cidx = lane + 32 * it;
+          const int r = cidx / (D / 8), c16 = cidx % (D / 8);
+          if (r >= n_valid)
+            *reinterpret_cast<uint4*>(vrow + (c16 >> 3) * L::kHalfBytes + (slice0 + r) * 128 + (c16 & 7) * 16) =
+                make_uint4(0, 0, 0, 0);
+        }
+        __syncwarp();
+      }
+      // ---- S[16 rows x 16 keys] = Q K^T ----
+      float sacc[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        // matrices: (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
+        const int key = slice0 + (mi >> 1) * 8 + mr;
+        const int chunk = 2 * ks + (mi & 1);
+        const uint32_t addr = sk + (chunk >> 3) * L::kHalfBytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(addr, b0, b1, b2, b3);
+        mma16816<BF16>(sacc[0], qa[ks], b0, b1);
+        mma16816<BF16>(sacc[1], qa[ks], b2, b3);
+      }
+      // ---- online softmax (rows qrow and qrow + 8; 4 lanes of a quad share a row) ----
+      float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const bool vis = nt * 8 + qcol + e < n_valid;
+          sacc[nt][e] = vis ? sacc[nt][e] * sc : -INFINITY;
+          sacc[nt][2 + e] = vis ? sacc[nt][2 + e] * sc : -INFINITY;
+          mx_lo = fmaxf(mx_lo, sacc[nt][e]);
+          mx_hi = fmaxf(mx_hi, sacc[nt][2 + e]);
+        }
+      }
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+      const float a_lo = (mn_lo == -INFINITY) ? 1.f : ex2f(m_lo - mn_lo);
+      const float a_hi = (mn_hi == -INFINITY) ? 1.f : ex2f(m_hi - mn_hi);
+      const float sub_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo;
+      const float sub_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;
+      m_lo = mn_lo;
+      m_hi = mn_hi;
+      uint32_t pa[4];
+      float rs_lo = 0.f, rs_hi = 0.f;
+      {
+        const float p00 = ex2f(sacc[0][0] - sub_lo), p01 = ex2f(sacc[0][1] - sub_lo);
+        const float p02 = ex2f(sacc[0][2] - sub_hi), p03 = ex2f(sacc[0][3] - sub_hi);
+        const float p10 = ex2f(sacc[1][0] - sub_lo), p11 = ex2f(sacc[1][1] - sub_lo);
+        const float p12 = ex2f(sacc[1][2] - sub_hi), p13 = ex2f(sacc[1][3] - sub_hi);
+        rs_lo = (p00 + p01) + (p10 + p11);
+        rs_hi = (p02 + p03) + (p12 + p13);
+        pa[0] = pack_p<BF16>(p00, p01);  // row lo, keys 0-7
+        pa[1] = pack_p<BF16>(p02, p03);  // row hi, keys 0-7
+        pa[2] = pack_p<BF16>(p10, p11);  // row lo, keys 8-15
+        pa[3] = pack_p<BF16>(p12, p13);  // row hi, keys 8-15
+      }
+      l_lo = l_lo * a_lo + rs_lo;  // per-lane partial sums, reduced across the quad at the end
+      l_hi = l_hi * a_hi + rs_hi;
+      // ---- O = a * O + P V ----
+#pragma unroll
+      for (int dp = 0; dp < kDTiles / 2; ++dp) {
+        // matrices: (keys 0-7, d tile 2dp), (keys 8-15, 2dp), (keys 0-7, 2dp+1), (keys 8-15, 2dp+1)
+        const int key = slice0 + (mi & 1) * 8 + mr;
+        const int chunk = 2 * dp + (mi >> 1);
+        const uint32_t addr = sv + (chunk >> 3) * L::kHalfBytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(addr, b0, b1, b2, b3);
+        float(&oa)[4] = o[2 * dp];
+        float(&ob)[4] = o[2 * dp + 1];
+        oa[0] *= a_lo; oa[1] *= a_lo; oa[2] *= a_hi; oa[3] *= a_hi;
+        ob[0] *= a_lo; ob[1] *= a_lo; ob[2] *= a_hi; ob[3] *= a_hi;
+        mma16816<BF16>(oa, pa, b0, b1);
+        mma16816<BF16>(ob, pa, b2, b3);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[stage]);
+      if (++stage == kDecStages) {
+        stage = 0;
+        phase ^= 1;
+      }
+    }
+    (void)ok;
+    // ---- quad-reduce the row sums, publish this warp's state ----
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    float* mo = merge_o + warp * kMaxRows * D;
+#pragma unroll
+    for (int dt = 0; dt < kDTiles; ++dt) {
+      *reinterpret_cast<float2*>(mo + qrow * D + dt * 8 + qcol) = make_float2(o[dt][0], o[dt][1]);
+      *reinterpret_cast<float2*>(mo + (qrow + 8) * D + dt * 8 + qcol) = make_float2(o[dt][2], o[dt][3]);
+    }
+    if ((lane & 3) == 0) {
+      float* ml = merge_ml + warp * kMaxRows * 2;
+      ml[qrow * 2 + 0] = m_lo;
+      ml[qrow * 2 + 1] = l_lo;
+      ml[(qrow + 8) * 2 + 0] = m_hi;
+      ml[(qrow + 8) * 2 + 1] = l_hi;
+    }
+    named_barrier_sync(1, 128);
+    // ---- merge the 4 warps in order 0..3 and write the partial triple ----
+    const int tid = threadIdx.x;  // 0..127
+    for (int r = 0; r < p.rows; ++r) {
+      float mstar = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) mstar = fmaxf(mstar, merge_ml[(w * kMaxRows + r) * 2]);
+      float lsum = 0.f;
+      float wgt[4];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float mw = merge_ml[(w * kMaxRows + r) * 2];
+        wgt[w] = (mw == -INFINITY) ? 0.f : ex2f(mw - mstar);
+        lsum += merge_ml[(w * kMaxRows + r) * 2 + 1] * wgt[w];
+      }
+      const int64_t prow = (((int64_t)b * p.Hkv + hk) * p.rows + r) * p.num_splits + split;
+      for (int d = tid; d < D; d += 128) {
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) acc += merge_o[(w * kMaxRows + r) * D + d] * wgt[w];
+        p.part_o[prow * D + d] = acc;
+      }
+      if (tid == 0) {
+        p.part_ml[prow * 2 + 0] = mstar;
+        p.part_ml[prow * 2 + 1] = lsum;
+      }
+    }
+  }
+}
+
+// One CTA per (batch, kv head, row): merges the valid splits in order and writes O.
+template <int D, bool BF16>
+__global__ void __launch_bounds__(D)
+decode_reduce_kernel(const DecParams p, void* __restrict__ out, int64_t os0, int64_t os1, int64_t os2) {
+  const int r = blockIdx.x % p.rows;
+  const int hk = (blockIdx.x / p.rows) % p.Hkv;
+  const int b = blockIdx.x / (p.rows * p.Hkv);
+  const int d = threadIdx.x;
+  int len = p.kv_lens ? p.kv_lens[b] : p.Skv;
+  len = max(0, min(len, p.Skv));
+  const int n_valid = len > 0 ? (len + p.chunk - 1) / p.chunk : 0;
+  const int64_t prow = (((int64_t)b * p.Hkv + hk) * p.rows + r) * p.num_splits;
+  float mstar = -INFINITY;
+  for (int s = 0; s < n_valid; ++s) mstar = fmaxf(mstar, p.part_ml[(prow + s) * 2]);
+  float lsum = 0.f, acc = 0.f;
+  for (int s = 0; s < n_valid; ++s) {
+    const float ms = p.part_ml[(prow + s) * 2];
+    const float w = (ms == -INFINITY) ? 0.f : ex2f(ms - mstar);
+    lsum += p.part_ml[(prow + s) * 2 + 1] * w;
+    acc += p.part_o[(prow + s) * D + d] * w;
+  }
+  const float v = lsum > 0.f ? acc / lsum : 0.f;
+  const int G = p.Hq / p.Hkv;
+  const int64_t st[3] = {os0, os1, os2};
+  const int64_t off = row_offset(r, hk, b, G, p.Sq, st) + d;
+  if constexpr (BF16)
+    reinterpret_cast<__nv_bfloat16*>(out)[off] = __float2bfloat16_rn(v);
+  else
+    reinterpret_cast<__half*>(out)[off] = __float2half_rn(v);
+}
+
+int choose_splits(int B, int Hkv, int Skv) {
+  const int sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
+  const int by_size = (Skv + 1023) / 1024;
+  const long pairs = (long)B * Hkv;
+  const int fill = (int)((2L * sms + pairs - 1) / pairs);
+  const int max_by_tile = (Skv + 127) / 128;
+  int s = by_size;
+  const int f = fill < max_by_tile ? fill : max_by_tile;
+  if (f > s) s = f;
+  if (s < 1) s = 1;
+  if (s > 64) s = 64;
+  return s;
+}
+
+int chunk_of(int Skv, int splits) {
+  const int c = (Skv + splits - 1) / splits;
+  return (c + kDecTile - 1) / kDecTile * kDecTile;
+}
+
+template <int D, bool BF16>
+int launch_decode(const void* Q, const void* K, const void* V, void* O, int B, int Hq, int Hkv, int Sq, int Skv,
+                  const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, float scale,
+                  const int32_t* kv_lens, int splits, float* part_o, float* part_ml, cudaStream_t stream) {
+  using L = DecSmem<D>;
+  auto kfn = decode_splitkv_kernel<D, BF16>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev & 63]) {
+    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return B200K_ECUDA;
+    }
+    configured[dev & 63] = true;
+  }
+  CUtensorMap tmK, tmV;
+  {
+    uint64_t dims[4] = {(uint64_t)D, (uint64_t)Skv, (uint64_t)Hkv, (uint64_t)B};
+    uint32_t box[4] = {64, (uint32_t)kDecTile, 1, 1};
+    uint64_t kstr[3] = {(uint64_t)ks[2] * 2, (uint64_t)ks[1] * 2, (uint64_t)ks[0] * 2};
+    uint64_t vstr[3] = {(uint64_t)vs[2] * 2, (uint64_t)vs[1] * 2, (uint64_t)vs[0] * 2};
+    int r;
+    if ((r = encode_tmap_16bit(&tmK, K, 4, dims, kstr, box, true))) return r;
+    if ((r = encode_tmap_16bit(&tmV, V, 4, dims, vstr, box, true))) return r;
+  }
+  DecParams p;
+  p.q = Q;
+  p.q_strides[0] = qs[0];
+  p.q_strides[1] = qs[1];
+  p.q_strides[2] = qs[2];
+  p.kv_lens = kv_lens;
+  p.part_o = part_o;
+  p.part_ml = part_ml;
+  p.B = B;
+  p.Hq = Hq;
+  p.Hkv = Hkv;
+  p.Sq = Sq;
+  p.Skv = Skv;
+  p.rows = Hq / Hkv * Sq;
+  p.num_splits = splits;
+  p.chunk = chunk_of(Skv, splits);
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status_ptr();
+  if (!p.status) return B200K_ECUDA;
+  dim3 grid(splits, Hkv, B);
+  kfn<<<grid, kDecThreads, L::kTotal, stream>>>(tmK, tmV, p);
+  count_launch();
+  int r = check_launch();
+  if (r) return r;
+  decode_reduce_kernel<D, BF16><<<B * Hkv * p.rows, D, 0, stream>>>(p, O, os[0], os[1], os[2]);
+  count_launch();
+  return check_launch();
+}
+
+}  // namespace
+}  // namespace b200k
+
+using namespace b200k;
+
+extern "C" int b200k_fmha_decode_auto_splits(int B, int Hkv, int Skv) {
+  if (B <= 0 || Hkv <= 0 || Skv <= 0) return 1;
+  return choose_splits(B, Hkv, Skv);
+}
+
+extern "C" size_t b200k_fmha_decode_workspace_bytes(int B, int Hq, int Hkv, int Sq, int Skv, int D, int num_splits) {
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0 || D <= 0 || Hq % Hkv) return 0;
+  const int splits = num_splits > 0 ? num_splits : choose_splits(B, Hkv, Skv);
+  const size_t rows = (size_t)B * Hkv * (size_t)(Hq / Hkv * Sq);
+  return rows * splits * (size_t)(D + 2) * sizeof(float);
+}
+
+extern "C" int b200k_fmha_decode_splitkv(const void* Q, const void* K, const void* V, void* O, int B, int Hq, int Hkv,
+                                         int Sq, int Skv, int D, const int64_t q_strides[3],
+                                         const int64_t k_strides[3], const int64_t v_strides[3],
+                                         const int64_t o_strides[3], float scale, const int32_t* kv_lens,
+                                         int num_splits, int dtype, void* workspace, size_t workspace_bytes,
+                                         b200k_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (dtype != B200K_F16 && dtype != B200K_BF16) return B200K_EDTYPE;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0 || Hq % Hkv != 0) return B200K_ESHAPE;
+  if (D != 64 && D != 128) return B200K_EHEADDIM;
+  if (Hq / Hkv * Sq > kMaxRows) return B200K_ESHAPE;  // more rows per KV head than one MMA tile
+  if (!Q || !K || !V || !O || !q_strides || !k_strides || !v_strides || !o_strides) return B200K_EARG;
+  if (!(scale > 0.f) || num_splits < 0 || num_splits > 1024) return B200K_EARG;
+  auto ok16 = [](const void* ptr, const int64_t* st) {
+    return aligned16(ptr) && st[0] % 8 == 0 && st[1] % 8 == 0 && st[2] % 8 == 0;
+  };
+  if (!ok16(K, k_strides) || !ok16(V, v_strides)) return B200K_EALIGN;
+  // q is read with 4-byte loads, o written element-wise: even strides suffice for q
+  if ((reinterpret_cast<uintptr_t>(Q) & 3) || q_strides[0] % 2 || q_strides[1] % 2 || q_strides[2] % 2)
+    return B200K_EALIGN;
+  if (!b200k_device_supported()) return B200K_ENOGPU;
+  const int splits = num_splits > 0 ? num_splits : choose_splits(B, Hkv, Skv);
+  const size_t need = b200k_fmha_decode_workspace_bytes(B, Hq, Hkv, Sq, Skv, D, splits);
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15)) return B200K_EWORKSPACE;
+  const size_t rows = (size_t)B * Hkv * (size_t)(Hq / Hkv * Sq);
+  float* part_o = reinterpret_cast<float*>(workspace);
+  float* part_ml = part_o + rows * splits * D;
+  const bool bf16 = dtype == B200K_BF16;
+#define B200K_DECODE(DD, BF)                                                                                     \
+  launch_decode<DD, BF>(Q, K, V, O, B, Hq, Hkv, Sq, Skv, q_strides, k_strides, v_strides, o_strides, scale, kv_lens, \
+                        splits, part_o, part_ml, stream)
+  if (D == 128) return bf16 ? B200K_DECODE(128, true) : B200K_DECODE(128, false);
+  return bf16 ? B200K_DECODE(64, true) : B200K_DECODE(64, false);
+#undef B200K_DECODE
+}
