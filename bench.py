@@ -1,0 +1,356 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 kernels: one JSON line on stdout.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline metric: TFLOP/s of the LLM-projection GEMM (bf16, M=8192 tokens against
+the Llama-2-7B-shaped 4096x11008 weight, fp32 accumulate), the largest single-GPU
+case of the GEMM sweep.  A step is one pass of that GEMM over synthetic
+operands (A ~ N(0,1), W ~ N(0,0.02)).  `value` is timed with the operands resident
+in HBM; `e2e` times the reference-facing call `gemm_unified.ops.fine_gemm` with
+HOST operands (pinned), host->device and device->host copies inside the timed
+region.  Operands + output are 334 MB per step, larger than the 126 MB L2.
+
+The same line carries, under "extra", the causal FMHA prefill configuration
+(fp16, B=1, 32/8 heads, s=4096, d=128; TFLOP/s with the causal half counted
+once) and the split-KV decode configuration (fp16, B=64, s_q=1, 32/8 heads,
+d=128, KV lengths uniform in [512, 32768]; GB/s of valid K+V bytes).
+
+With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank owns
+one N-tile slab of a weight that is N times wider (per-GPU work fixed, "weak"),
+no data-path collective; the time is the max over ranks.
+
+--impl reference times the reference's CPU path for the same math (fp32
+torch.matmul on the host cores: the function the reference's own check uses,
+kernels/gemm/test/correct.py:9-16) on a bounded row slab of the same GEMM.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "understanding-gpu-architecture-implications-on-llm-serving-workloads_b200")
+for _p in (ROOT, PKG):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+M, K, N = 8192, 4096, 11008
+WORKLOAD = f"llm_projection_gemm_bf16_M{M}_K{K}_N{N}"
+METRIC = "gemm_tflops"
+UNIT = "TFLOP/s"
+FLOPS_PER_STEP = 2.0 * M * N * K
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the GEMM kernel on this
+# workload, from the ncu capture summarised in profiles/ (None until captured)
+NCU_TRAFFIC_BYTES = None
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return {"tflops": float(d["bf16_tflops"]), "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    except Exception:
+        return {"tflops": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def time_cuda(fn, steps: int, warmup: int, barrier=None) -> float:
+    """Seconds for `steps` calls of fn, CUDA events on the current stream, after warm-up."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    return e0.elapsed_time(e1) / 1e3
+
+
+# ------------------------------------------------------------------ CPU baseline / reference arm
+def cpu_gemm_sample(target_seconds: float, repeats: int = 1):
+    """Times the oracle's fp32 CPU matmul on a row slab of the same GEMM (full K and N)
+    sized for about `target_seconds`; returns (TFLOP/s, threads, description)."""
+    from oracle import oracle
+    from b200k import inputs
+    threads = torch.get_num_threads()
+    g = torch.Generator().manual_seed(1)
+    w = (torch.randn(K, N, generator=g) * 0.02).to(torch.bfloat16)
+    probe_rows = 64
+    a = torch.randn(probe_rows, K, generator=g).to(torch.bfloat16)
+    oracle.gemm_ref(a, w)  # warm-up (thread pool, page faults)
+    t0 = time.perf_counter()
+    oracle.gemm_ref(a, w)
+    probe = max(time.perf_counter() - t0, 1e-4)
+    rows = int(min(M, max(probe_rows, probe_rows * target_seconds / probe)))
+    rows = max(64, rows // 64 * 64)
+    a = torch.randn(rows, K, generator=g).to(torch.bfloat16)
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        oracle.gemm_ref(a, w)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    tflops = 2.0 * rows * N * K / best / 1e12
+    del inputs
+    return tflops, threads, f"fp32 torch.matmul on CPU, {rows} of {M} rows x full K={K}, N={N} (bf16-rounded operands widened to fp32)", rows, best
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    steps, warmup = args.steps, args.warmup
+    from oracle import oracle
+    g = torch.Generator().manual_seed(1)
+    w = (torch.randn(K, N, generator=g) * 0.02).to(torch.bfloat16)
+    # slab sized so that one step is ~1.5 s of CPU work
+    tflops0, threads, _, _, _ = cpu_gemm_sample(1.5)
+    rows = int(min(M, max(64, (1.5 * tflops0 * 1e12 / (2.0 * N * K)) // 64 * 64)))
+    a = torch.randn(rows, K, generator=g).to(torch.bfloat16)
+    for _ in range(warmup):
+        oracle.gemm_ref(a, w)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.gemm_ref(a, w)
+    dt = time.perf_counter() - t0
+    value = 2.0 * rows * N * K * steps / dt / 1e12
+    sample = f"each step: fp32 torch.matmul on CPU of {rows} of {M} rows x full K={K}, N={N}"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample_rows": rows},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ------------------------------------------------------------------ our arm
+def run_ours(args):
+    import torch.distributed as dist
+    from b200k import _lib, fmha, gemm, inputs
+    import gemm_unified
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    distributed = world > 1
+    if distributed:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.lib()  # fail loudly here if the extension is missing
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+
+    def max_over_ranks(seconds: float) -> float:
+        if not distributed:
+            return seconds
+        t = torch.tensor([seconds], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    steps, warmup = args.steps, max(args.warmup, 3)
+    peaks = measured_peaks()
+
+    # ---- headline GEMM: rank r owns column slab r of a weight N*world wide (weak scaling) ----
+    a = inputs.device_randn16((M, K), 100 + rank, 1.0, torch.bfloat16, dev)
+    w = inputs.device_randn16((K, N), 200 + rank, 0.02, torch.bfloat16, dev)
+    c = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+
+    def step():
+        gemm.gemm(a, w, out=c)
+
+    sampler = ClockSampler(local_rank)
+    launches0 = _lib.launch_count()
+    if rank == 0:
+        sampler.start()
+    secs = max_over_ranks(time_cuda(step, steps, warmup, barrier))
+    launches = _lib.launch_count() - launches0 - warmup
+    clocks = sampler.stop() if rank == 0 else None
+    code, detail = _lib.device_status()
+    if code != 0:
+        raise SystemExit(f"device status {code} detail {detail:#x} after the timed region")
+    value = world * FLOPS_PER_STEP * steps / secs / 1e12
+    kernel_tflops = FLOPS_PER_STEP * steps / secs / 1e12  # per GPU == the kernel's own rate
+
+    # ---- e2e: reference-facing op, host operands, copies inside the timed region ----
+    a_h = a.cpu().pin_memory()
+    w_h = w.cpu().pin_memory()
+    c_h = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    a_d = torch.empty_like(a)
+    w_d = torch.empty_like(w)
+
+    def e2e_step():
+        a_d.copy_(a_h, non_blocking=True)
+        w_d.copy_(w_h, non_blocking=True)
+        out = gemm_unified.ops.fine_gemm(a_d, w_d, 12)
+        c_h.copy_(out, non_blocking=True)
+
+    e2e_steps = max(3, min(steps, 10))
+    e2e_secs = max_over_ranks(time_cuda(e2e_step, e2e_steps, 3, barrier))
+    e2e_value = world * FLOPS_PER_STEP * e2e_steps / e2e_secs / 1e12
+    h2d = a_h.numel() * 2 + w_h.numel() * 2
+    d2h = c_h.numel() * 2
+    del a_h, w_h, c_h, a_d, w_d
+
+    # ---- extra: FMHA prefill (causal, s=4096) and split-KV decode ----
+    extra = {}
+    try:
+        q, k, v = inputs.fmha_c3(dev)
+        o = torch.empty_like(q)
+        fsteps = max(steps, 10)
+        fsecs = max_over_ranks(time_cuda(lambda: fmha.fmha_fwd(q, k, v, causal=True, out=o), fsteps, warmup, barrier))
+        fflops = 4.0 * 1 * 32 * 4096 * 4096 * 128 * 0.5
+        tf = world * fflops * fsteps / fsecs / 1e12
+        extra["fmha_prefill"] = {
+            "workload": "causal_fmha_fp16_B1_H32_8_S4096_D128", "value": tf, "unit": "TFLOP/s",
+            "ms": fsecs / fsteps * 1e3, "flops_convention": "executed (causal half counted once)",
+            "reference_convention_tflops": 2 * tf,
+            "roofline": {"bound": "tensor", "achieved": tf / world, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                         "frac": tf / world / peaks["tflops"], "traffic": None}}
+        del q, k, v, o
+        B, Hq, Hkv, Skv, D = 64, 32, 8, 32768, 128
+        lens = inputs.decode_lens(B).to(dev)
+        qd = inputs.device_randn16((B, Hq, 1, D), 7, 1.0, torch.float16, dev)
+        kd = inputs.device_randn16((B, Hkv, Skv, D), 8, 1.0, torch.float16, dev)
+        vd = inputs.device_randn16((B, Hkv, Skv, D), 9, 1.0, torch.float16, dev)
+        od = torch.empty_like(qd)
+        ws = fmha.decode_workspace(B, Hq, Hkv, 1, Skv, D, 0, dev)
+        dsteps = max(steps, 10)
+        dsecs = max_over_ranks(time_cuda(
+            lambda: fmha.fmha_decode(qd, kd, vd, kv_lens=lens, out=od, workspace=ws), dsteps, warmup, barrier))
+        dbytes = float(lens.sum().item()) * Hkv * D * 2 * 2 + 2.0 * B * Hq * D * 2
+        gbs = world * dbytes * dsteps / dsecs / 1e9
+        extra["decode_splitkv"] = {
+            "workload": "decode_fp16_B64_Sq1_H32_8_D128_kvlen_U512_32768", "value": gbs, "unit": "GB/s",
+            "ms": dsecs / dsteps * 1e3, "bytes": "valid K+V once, q and o once",
+            "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / world / peaks["hbm_gbs"], "traffic": None}}
+        del qd, kd, vd, od, ws
+    except Exception as exc:  # the headline number stands even if an extra fails
+        extra["error"] = repr(exc)[:300]
+
+    # ---- CPU baseline on rank 0 at N=1 ----
+    cpu = None
+    if world == 1 and rank == 0 and not args.no_cpu_baseline:
+        tflops, threads, sample, _, _ = cpu_gemm_sample(10.0)
+        cpu = {"value": tflops, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
+
+    if rank == 0:
+        algorithmic = "flops"
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": secs / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "accumulate": "f32", "l2": "operands+output 334 MB per step > 126 MB L2",
+                       "sharding": "rank r owns N-tile slab r of a weight N*n_gpus wide; no data-path collective",
+                       "peak_source": peaks["source"]},
+            "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                         "frac": kernel_tflops / peaks["tflops"], "traffic": NCU_TRAFFIC_BYTES,
+                         "algorithmic": algorithmic, "frac_of_nominal_2250": kernel_tflops / 2250.0},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "api": "gemm_unified.ops.fine_gemm(a, b, 12)"},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "extra": extra,
+        }
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "ours" and args.gpus != world and args.gpus > 1:
+        raise SystemExit(f"--gpus {args.gpus} needs torch.distributed.run with --nproc-per-node {args.gpus} "
+                         f"(WORLD_SIZE is {world})")
+    return run_reference(args) if args.impl == "reference" else run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -143,6 +143,15 @@ uint64_t b200k_launch_count(void);
 /* 1 when the current device is compute capability 10.x, else 0. */
 int b200k_device_supported(void);
 
+/*
+ * Introspection for tests (no GPU needed): the exact bit patterns the kernels
+ * hand to tcgen05.mma.  smem descriptor: 128-byte swizzle, version 1;
+ * instruction descriptor: kind::f16, fp32 accumulate, major 0 = K, 1 = MN.
+ * The reference has no counterpart (its kernels use WMMA fragments).
+ */
+uint64_t b200k_debug_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes);
+uint32_t b200k_debug_instr_desc(int dtype, int a_major, int b_major, int M, int N);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,147 @@
+"""CPU tests of the oracle itself: pinned against the golden fixtures (outputs of the
+reference test scripts' own oracle functions, tests/golden/make_golden.py), and its
+three statements (closed formula, online recurrences in numpy, C restatement) against
+each other."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+ORACLE_DIR = os.path.join(os.path.dirname(GOLDEN), "..", "oracle")
+
+
+def _load16(arr, bf16):
+    t = torch.from_numpy(arr)
+    return t.view(torch.bfloat16) if bf16 else t
+
+
+@pytest.fixture(scope="module")
+def c_oracle():
+    path = os.path.join(ORACLE_DIR, "_build", "liboracle.so")
+    if not os.path.exists(path):
+        import subprocess
+        subprocess.run(["make", "-C", ORACLE_DIR], check=True, capture_output=True)
+    lib = ctypes.CDLL(path)
+    lib.oracle_gemm.restype = ctypes.c_int
+    lib.oracle_fmha.restype = ctypes.c_int
+    return lib
+
+
+def _c_gemm(lib, a, b):
+    M, K = a.shape
+    N = b.shape[1]
+    out = np.empty((M, N), dtype=np.float32)
+    bf16 = a.dtype == torch.bfloat16
+    a16 = a.contiguous().view(torch.int16).numpy()
+    b16 = b.contiguous().view(torch.int16).numpy()
+    rc = lib.oracle_gemm(a16.ctypes.data_as(ctypes.c_void_p), b16.ctypes.data_as(ctypes.c_void_p),
+                         out.ctypes.data_as(ctypes.c_void_p), M, N, K, int(bf16))
+    assert rc == 0
+    return torch.from_numpy(out)
+
+
+def _c_fmha(lib, q, k, v, causal, lens=None):
+    B, Hq, Sq, D = q.shape
+    Hkv, Skv = k.shape[1], k.shape[2]
+    out = np.empty((B, Hq, Sq, D), dtype=np.float32)
+    bf16 = q.dtype == torch.bfloat16
+    arrs = [t.contiguous().view(torch.int16).numpy() for t in (q, k, v)]
+    lp = None
+    if lens is not None:
+        lens_np = np.asarray(lens, dtype=np.int32)
+        lp = lens_np.ctypes.data_as(ctypes.c_void_p)
+    rc = lib.oracle_fmha(*[x.ctypes.data_as(ctypes.c_void_p) for x in arrs], out.ctypes.data_as(ctypes.c_void_p),
+                         B, Hq, Hkv, Sq, Skv, D, int(causal), lp, int(bf16))
+    assert rc == 0
+    return torch.from_numpy(out)
+
+
+def test_gemm_golden(c_oracle):
+    z = np.load(os.path.join(GOLDEN, "gemm_seed0_256.npz"))
+    a, b, expected = torch.from_numpy(z["a"]), torch.from_numpy(z["b"]), torch.from_numpy(z["expected"])
+    assert torch.allclose(oracle.gemm_ref(a, b), expected, rtol=1e-5, atol=1e-4)
+    assert torch.allclose(_c_gemm(c_oracle, a, b), expected, rtol=1e-5, atol=1e-3)
+    # the reference's own acceptance window for its kernels (kernels/gemm/test/correct.py:16)
+    assert torch.allclose(oracle.gemm_ref(a, b).half().float(), expected, rtol=1e-1, atol=1e-1)
+
+
+def test_gemm_loops_restatement():
+    g = torch.Generator().manual_seed(3)
+    a = torch.randn(9, 13, generator=g).half()
+    b = torch.randn(13, 7, generator=g).half()
+    loops = oracle.gemm_ref_loops(a.numpy(), b.numpy())
+    assert np.allclose(loops, oracle.gemm_ref(a, b).double().numpy(), rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("name", ["fmha_seed42_mha_causal_f16", "fmha_seed42_gqa_causal_f16",
+                                  "fmha_seed42_gqa_full_bf16", "fmha_seed42_gqa_decode_f16"])
+def test_fmha_golden(c_oracle, name):
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    bf16 = bool(z["bf16"])
+    q, k, v = (_load16(z[x], bf16) for x in ("q", "k", "v"))
+    causal = bool(z["causal"])
+    expected = torch.from_numpy(z["expected"])
+    # the golden decode case has Sq = 1 < Skv and is non-causal, so alignment is moot
+    got = oracle.fmha_ref(q, k, v, causal=causal)
+    assert torch.allclose(got, expected, rtol=1e-5, atol=2e-6)
+    got_c = _c_fmha(c_oracle, q, k, v, causal)
+    assert torch.allclose(got_c, expected, rtol=1e-4, atol=5e-6)
+    online = oracle.fmha_ref_online(q[0].float().numpy(), k[0].float().numpy(), v[0].float().numpy(), causal=causal)
+    assert np.allclose(online, expected[0].numpy(), rtol=1e-4, atol=5e-6)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape", [(2, 4, 2, 70, 70, 64), (1, 8, 8, 33, 200, 128), (1, 4, 1, 1, 150, 128)])
+def test_fmha_formula_vs_sdpa_and_c(c_oracle, shape, causal):
+    """Closed formula == torch SDPA (square, causal/full, GQA) == C restatement, N(0,1) inputs."""
+    B, Hq, Hkv, Sq, Skv, D = shape
+    g = torch.Generator().manual_seed(sum(shape))
+    q = torch.randn(B, Hq, Sq, D, generator=g).half()
+    k = torch.randn(B, Hkv, Skv, D, generator=g).half()
+    v = torch.randn(B, Hkv, Skv, D, generator=g).half()
+    ref = oracle.fmha_ref(q, k, v, causal=causal)
+    assert torch.allclose(_c_fmha(c_oracle, q, k, v, causal), ref, rtol=1e-4, atol=2e-5)
+    if Sq == Skv or not causal:
+        rep = Hq // Hkv
+        sdpa = torch.nn.functional.scaled_dot_product_attention(
+            q.float(), k.float().repeat_interleave(rep, 1), v.float().repeat_interleave(rep, 1), is_causal=causal)
+        assert torch.allclose(ref, sdpa, rtol=1e-4, atol=2e-5)
+
+
+def test_fmha_kv_lens_and_nan_padding(c_oracle):
+    g = torch.Generator().manual_seed(9)
+    q = torch.randn(3, 4, 1, 64, generator=g).half()
+    k = torch.randn(3, 2, 90, 64, generator=g).half()
+    v = torch.randn(3, 2, 90, 64, generator=g).half()
+    lens = [1, 37, 90]
+    ref = torch.stack([oracle.fmha_ref(q[b:b + 1], k[b:b + 1, :, :n], v[b:b + 1, :, :n])[0]
+                       for b, n in enumerate(lens)])
+    k2, v2 = k.clone(), v.clone()
+    for b, n in enumerate(lens):
+        k2[b, :, n:] = float("nan")
+        v2[b, :, n:] = float("nan")
+    got = oracle.fmha_ref(q, k2, v2, kv_lens=torch.tensor(lens))
+    assert torch.allclose(got, ref, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(_c_fmha(c_oracle, q, k2, v2, False, lens), ref, rtol=1e-4, atol=2e-5)
+
+
+def test_causal_bottom_right_and_empty_rows():
+    """Sq > Skv under the causal rule: rows that see no key give zeros."""
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(1, 1, 6, 64, generator=g).half()
+    k = torch.randn(1, 1, 4, 64, generator=g).half()
+    v = torch.randn(1, 1, 4, 64, generator=g).half()
+    out = oracle.fmha_ref(q, k, v, causal=True)
+    assert torch.count_nonzero(out[0, 0, :2]) == 0          # rows 0, 1 see keys j <= i - 2: none
+    assert torch.allclose(out[0, 0, 2], v[0, 0, 0].float())  # row 2 sees key 0 only
+
+
+def test_metrics():
+    x = torch.ones(4, 4)
+    assert oracle.rel_frobenius(x * 1.01, x) == pytest.approx(0.01, rel=1e-6)
+    assert oracle.max_abs(x + 0.5, x) == pytest.approx(0.5)

@@ -1,0 +1,103 @@
+"""Partitioning of the two paths over the GPUs of one node (one process per GPU).
+
+The reference has no multi-GPU code at all (no torch.distributed / NCCL call site);
+this is new work that shards only where the math is independent:
+  * GEMM: the weight B[K,N] is cut into contiguous column slabs whose widths are
+    multiples of the 128-column tile, rank r computes C[:, slab_r]; a collective
+    (all-gather over NCCL) is needed only when the full C must be reassembled.
+  * FMHA prefill: (batch, KV-head group) pairs are independent; no collective.
+  * Decode: sequences are independent; they are assigned greedily, longest first,
+    to the rank with the least total KV length; no collective.
+All functions here are pure host logic (testable on CPU with the gloo backend).
+"""
+from __future__ import annotations
+
+from typing import List, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+TILE_N = 128
+
+
+def gemm_column_slabs(N: int, world: int, tile: int = TILE_N) -> List[Tuple[int, int]]:
+    """[start, end) column ranges, one per rank: whole tiles spread as evenly as possible,
+    the ragged tail (N % tile) goes to the last rank that owns any tile."""
+    n_tiles = (N + tile - 1) // tile
+    base, extra = divmod(n_tiles, world)
+    out, t0 = [], 0
+    for r in range(world):
+        t1 = t0 + base + (1 if r < extra else 0)
+        out.append((min(t0 * tile, N), min(t1 * tile, N)))
+        t0 = t1
+    return out
+
+
+def head_shards(B: int, Hq: int, Hkv: int, world: int) -> List[List[Tuple[int, int, int]]]:
+    """Work items (batch, first kv head, number of kv heads) per rank.  KV-head groups are
+    kept whole (a query head and its KV head never separate); heads are split first,
+    then batches."""
+    items = [(b, hk) for b in range(B) for hk in range(Hkv)]
+    per, extra = divmod(len(items), world)
+    shards, i = [], 0
+    for r in range(world):
+        n = per + (1 if r < extra else 0)
+        mine = items[i:i + n]
+        i += n
+        merged: List[Tuple[int, int, int]] = []
+        for (b, hk) in mine:
+            if merged and merged[-1][0] == b and merged[-1][1] + merged[-1][2] == hk:
+                merged[-1] = (b, merged[-1][1], merged[-1][2] + 1)
+            else:
+                merged.append((b, hk, 1))
+        shards.append(merged)
+    return shards
+
+
+def balance_sequences(kv_lens: Sequence[int], world: int) -> List[List[int]]:
+    """Greedy longest-first assignment of sequence indices to ranks by total KV length."""
+    order = sorted(range(len(kv_lens)), key=lambda i: (-int(kv_lens[i]), i))
+    loads = [0] * world
+    out: List[List[int]] = [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda j: (loads[j], j))
+        out[r].append(i)
+        loads[r] += int(kv_lens[i])
+    for lst in out:
+        lst.sort()
+    return out
+
+
+def all_gather_columns(c_local: torch.Tensor, slabs: Sequence[Tuple[int, int]], group=None) -> torch.Tensor:
+    """Reassembles C[M,N] from per-rank column slabs (the one collective of the GEMM path).
+    Slabs may differ in width; they are gathered padded to the widest and trimmed."""
+    world = dist.get_world_size(group)
+    M = c_local.size(0)
+    widths = [e - s for (s, e) in slabs]
+    wmax = max(widths)
+    send = c_local
+    if c_local.size(1) != wmax:
+        send = c_local.new_zeros((M, wmax))
+        send[:, :c_local.size(1)] = c_local
+    send = send.contiguous()
+    recv = send.new_empty((world * M, wmax))  # rank-major concatenation along dim 0
+    dist.all_gather_into_tensor(recv, send, group=group)
+    recv = recv.view(world, M, wmax)
+    out = send.new_empty((M, slabs[-1][1]))
+    for r, (s, e) in enumerate(slabs):
+        out[:, s:e] = recv[r, :, :e - s]
+    return out
+
+
+def sharded_gemm(a: torch.Tensor, b_full: torch.Tensor, gather: bool, matmul, group=None):
+    """Rank-local slab of a @ b_full (and the gathered full product when `gather`).
+    `matmul(a, b_slab)` is the local kernel (the library GEMM on GPU; torch.matmul in
+    the CPU tests of this host logic)."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    slabs = gemm_column_slabs(b_full.size(1), world)
+    s, e = slabs[rank]
+    c_local = matmul(a, b_full[:, s:e]) if e > s else a.new_empty((a.size(0), 0))
+    if not gather:
+        return c_local, slabs
+    return all_gather_columns(c_local, slabs, group), slabs

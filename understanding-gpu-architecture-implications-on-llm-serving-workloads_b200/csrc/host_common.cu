@@ -1,5 +1,6 @@
 // Host-side helpers: tensor-map encoding, device status word, error strings.
 #include "host_common.h"
+#include "ptx.cuh"
 
 #include <atomic>
 #include <mutex>
@@ -146,6 +147,14 @@ int b200k_device_supported(void) {
     return 0;
   }
   return b200k::dev_info().cc_major == 10 ? 1 : 0;
+}
+
+uint64_t b200k_debug_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return b200k::make_smem_desc_sw128(smem_addr, lbo_bytes, sbo_bytes);
+}
+
+uint32_t b200k_debug_instr_desc(int dtype, int a_major, int b_major, int M, int N) {
+  return b200k::make_idesc_f16(dtype == B200K_BF16 ? 1 : 0, a_major, b_major, M, N);
 }
 
 }  // extern "C"
