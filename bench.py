@@ -64,56 +64,72 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and clock-event (throttle) reasons of one GPU every few
+    milliseconds through NVML while the timed region runs (the same counters
+    `nvidia-smi --query-gpu=clocks.sm,clocks_event_reasons.*` prints; a polling
+    thread is used because the timed region is shorter than nvidia-smi's period)."""
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
-    def __init__(self, index: int):
-        self.index = index
-        self.proc = None
-        self.lines = []
+    def __init__(self, index: int, period_s: float = 0.002):
+        self.index, self.period = index, period_s
+        self.samples, self.mask = [], 0
+        self.sm_max = None
+        self._stop = threading.Event()
+        self.thread = None
+        self.marks = {}
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            idx = self.index
+            if visible:
+                ids = [x for x in visible.split(",") if x.strip()]
+                if self.index < len(ids) and ids[self.index].strip().isdigit():
+                    idx = int(ids[self.index])
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(idx)
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
         except Exception:
-            self.proc = None
+            self.nvml = None
+            return
+        self.thread = threading.Thread(target=self._poll, daemon=True)
+        self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+    def mark(self, name: str):
+        self.marks[name] = time.perf_counter()
+
+    def _poll(self):
+        n = self.nvml
+        while not self._stop.is_set():
+            try:
+                mhz = float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                try:
+                    reasons = int(n.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                except Exception:
+                    reasons = int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                self.samples.append((time.perf_counter(), mhz, reasons))
+            except Exception:
+                pass
+            time.sleep(self.period)
 
     def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 6:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[2:6]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        if not self.thread:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "source": "unavailable"}
+        self._stop.set()
+        self.thread.join(timeout=2)
+        t0, t1 = self.marks.get("begin", 0.0), self.marks.get("end", float("inf"))
+        inside = [(m, r) for (t, m, r) in self.samples if t0 <= t <= t1]
+        mask = 0
+        for _, r in inside:
+            mask |= r
+        reasons = sorted(name for name, bit in self.REASONS.items() if mask & bit)
+        return {"sm_mhz": statistics.median(m for m, _ in inside) if inside else None, "sm_max_mhz": self.sm_max,
+                "reasons": reasons, "samples": len(inside), "source": "nvml polling during the timed region"}
 
 
-def time_cuda(fn, steps: int, warmup: int, barrier=None) -> float:
+def time_cuda(fn, steps: int, warmup: int, barrier=None, sampler=None) -> float:
     """Seconds for `steps` calls of fn, CUDA events on the current stream, after warm-up."""
     for _ in range(warmup):
         fn()
@@ -123,11 +139,15 @@ def time_cuda(fn, steps: int, warmup: int, barrier=None) -> float:
     torch.cuda.synchronize()
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)
+    if sampler:
+        sampler.mark("begin")
     e0.record()
     for _ in range(steps):
         fn()
     e1.record()
     torch.cuda.synchronize()
+    if sampler:
+        sampler.mark("end")
     if barrier:
         barrier()
     return e0.elapsed_time(e1) / 1e3
@@ -194,6 +214,44 @@ def run_reference(args):
     return 0
 
 
+# ------------------------------------------------------------------ small cases for ncu captures
+def run_profile_case(args):
+    """Runs ONE hot path a few times (inputs larger than L2, at most ~2 GB on the device, nothing
+    else on the GPU) so that a profiler capture of it ends by itself; prints a short JSON line."""
+    from b200k import _lib, fmha, gemm, inputs
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    case, n = args.profile_case, max(1, args.steps)
+    if case == "gemm":
+        a = inputs.device_randn16((M, K), 100, 1.0, torch.bfloat16, dev)
+        w = inputs.device_randn16((K, N), 200, 0.02, torch.bfloat16, dev)
+        c = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        fn = lambda: gemm.gemm(a, w, out=c, variant=args.variant)
+        work, unit = FLOPS_PER_STEP / 1e12, "TFLOP/s"
+    elif case == "fmha":
+        q, k, v = inputs.fmha_c3(dev)
+        o = torch.empty_like(q)
+        fn = lambda: fmha.fmha_fwd(q, k, v, causal=True, out=o)
+        work, unit = 4.0 * 32 * 4096 * 4096 * 128 * 0.5 / 1e12, "TFLOP/s"
+    elif case == "decode":
+        B, Hq, Hkv, Skv, D = 16, 32, 8, 32768, 128   # a quarter of the batch: 2 GiB of K+V
+        lens = inputs.decode_lens(64)[:B].to(dev)
+        q = inputs.device_randn16((B, Hq, 1, D), 7, 1.0, torch.float16, dev)
+        k = inputs.device_randn16((B, Hkv, Skv, D), 8, 1.0, torch.float16, dev)
+        v = inputs.device_randn16((B, Hkv, Skv, D), 9, 1.0, torch.float16, dev)
+        o = torch.empty_like(q)
+        ws = fmha.decode_workspace(B, Hq, Hkv, 1, Skv, D, 0, dev)
+        fn = lambda: fmha.fmha_decode(q, k, v, kv_lens=lens, out=o, workspace=ws)
+        work, unit = (float(lens.sum().item()) * Hkv * D * 4 + 2.0 * B * Hq * D * 2) / 1e9, "GB/s"
+    else:
+        raise SystemExit(f"unknown --profile-case {case}")
+    secs = time_cuda(fn, n, max(1, args.warmup))
+    code, detail = _lib.device_status()
+    print(json.dumps({"profile_case": case, "launch_ms": secs / n * 1e3, "rate": work * n / secs, "unit": unit,
+                      "device_status": code}), flush=True)
+    return 0 if code == 0 else 1
+
+
 # ------------------------------------------------------------------ our arm
 def run_ours(args):
     import torch.distributed as dist
@@ -239,7 +297,7 @@ def run_ours(args):
     launches0 = _lib.launch_count()
     if rank == 0:
         sampler.start()
-    secs = max_over_ranks(time_cuda(step, steps, warmup, barrier))
+    secs = max_over_ranks(time_cuda(step, steps, warmup, barrier, sampler if rank == 0 else None))
     launches = _lib.launch_count() - launches0 - warmup
     clocks = sampler.stop() if rank == 0 else None
     code, detail = _lib.device_status()
@@ -344,11 +402,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "fmha", "decode"],
+                    help="run only this path on a capture-sized case (for ncu); prints its own short line")
+    ap.add_argument("--variant", type=int, default=0, help="GEMM kernel variant for --profile-case gemm")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "ours" and args.gpus != world and args.gpus > 1:
         raise SystemExit(f"--gpus {args.gpus} needs torch.distributed.run with --nproc-per-node {args.gpus} "
                          f"(WORLD_SIZE is {world})")
+    if args.profile_case:
+        return run_profile_case(args)
     return run_reference(args) if args.impl == "reference" else run_ours(args)
 
 
