@@ -36,7 +36,8 @@ enum {
   B200K_ETIMEOUT = -7,   /* a bounded device-side wait expired (see b200k_device_status) */
   B200K_ETMAP = -8,      /* cuTensorMapEncodeTiled refused the operand */
   B200K_EARG = -9,       /* other invalid argument (e.g. causal together with decode) */
-  B200K_ENOGPU = -10     /* no sm_100 device is current */
+  B200K_ENOGPU = -10,    /* no sm_100 device is current */
+  B200K_ESCRATCH = -11   /* problem needs more than the library's fixed built-in scratch */
 };
 
 enum { B200K_F16 = 0, B200K_BF16 = 1 };
@@ -125,6 +126,41 @@ size_t b200k_fmha_decode_workspace_bytes(int B, int Hq, int Hkv, int Sq, int Skv
 
 /* The split count b200k_fmha_decode_splitkv uses for num_splits = 0. */
 int b200k_fmha_decode_auto_splits(int B, int Hkv, int Skv);
+
+/*
+ * b200k_fmha_decode_splitkv for callers that cannot allocate device memory (a
+ * server with a memory pool fixed at start-up, a plugin that does not own the
+ * process's allocator, a latency-critical loop where cudaMalloc's implicit
+ * synchronisation is not acceptable).  Same arguments and result, but there is
+ * no workspace argument: the per-split partial results go to a scratch array
+ * built into the library image, b200k_fmha_decode_static_scratch_bytes() bytes
+ * (16 MiB) on every GPU that loads the library, held until the process exits.
+ * The call allocates nothing (no cudaMalloc / cudaFree / allocating library
+ * routine).
+ *   - Limit: B * Hq * Sq * splits * (D + 2) * 4 bytes must fit the scratch.  With
+ *     num_splits = 0 the split count is lowered until it fits; an explicit
+ *     num_splits that does not fit, or a problem that does not fit unsplit,
+ *     returns B200K_ESCRATCH and launches nothing.
+ *   - The first call on each device looks up the scratch array's device address
+ *     (one cudaGetSymbolAddress with that device current).  Make that first call
+ *     outside any stream capture.
+ *   - All calls on a device share the one array, and it keeps the previous
+ *     call's contents.  Nothing needs clearing (every slot that is read was
+ *     written by the same call), but two calls that overlap on the GPU (different
+ *     streams, or one thread per stream) race on it: serialise them.
+ * No counterpart in the reference, which has neither a split over keys nor a
+ * workspace.
+ */
+int b200k_fmha_decode_splitkv_static(const void* Q_device, const void* K_device,
+                                     const void* V_device, void* O_device,
+                                     int B, int Hq, int Hkv, int Sq, int Skv, int D,
+                                     const int64_t q_strides[3], const int64_t k_strides[3],
+                                     const int64_t v_strides[3], const int64_t o_strides[3],
+                                     float scale, const int32_t* kv_lens_device,
+                                     int num_splits, int dtype, b200k_stream_t stream);
+
+/* Size in bytes of the built-in scratch array of b200k_fmha_decode_splitkv_static. */
+size_t b200k_fmha_decode_static_scratch_bytes(void);
 
 /* Text for a return code. */
 const char* b200k_strerror(int code);

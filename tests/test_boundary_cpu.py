@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol():
 def test_strerror_and_codes():
     from b200k import _lib
     assert _lib.strerror(0) == "ok"
-    for code in range(-10, 0):
+    for code in range(-11, 0):
         assert "unknown" not in _lib.strerror(code)
     assert "unknown" in _lib.strerror(-99)
 

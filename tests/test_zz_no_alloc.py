@@ -1,0 +1,65 @@
+"""The allocation-free decode entry point, b200k_fmha_decode_splitkv_static.
+
+It exists for callers that may not allocate device memory while serving (a fixed
+memory pool, a plugin that does not own the allocator, a loop that cannot afford
+cudaMalloc's synchronisation): its split-KV partials live in a 16 MiB array built
+into the library instead of a caller workspace.  The test drives it through the C
+ABI directly (ctypes, raw device pointers) and compares with the ordinary entry
+point, which takes the workspace from the caller, on two calls in a row with
+different inputs, so stale contents of the shared array from the first call would
+show in the second.  This file sorts last so a run that stops at the first failure
+has already run every other test; it also passes when run alone."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _call_static(L, q, k, v, out, lens, splits):
+    from b200k import _lib
+    B, Hq, Sq, D = q.shape
+    return L.b200k_fmha_decode_splitkv_static(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, Hq, k.size(1), Sq, k.size(2), D,
+        _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(out), float(D) ** -0.5,
+        lens.data_ptr() if lens is not None else None, splits, _lib.F16,
+        torch.cuda.current_stream().cuda_stream)
+
+
+def test_static_scratch_matches_workspace_entry_point(cuda_device):
+    from b200k import _lib, fmha, inputs
+    L = _lib.lib()
+    assert L.b200k_fmha_decode_static_scratch_bytes() == 16 << 20
+    B, Hq, Hkv, Skv, D = 8, 32, 8, 4096, 128
+    lens_a = torch.tensor([4096, 1, 777, 2048, 4095, 64, 3000, 129], dtype=torch.int32, device=cuda_device)
+    lens_b = torch.tensor([5, 4096, 4096, 100, 1, 4000, 63, 2049], dtype=torch.int32, device=cuda_device)
+    for seed, lens, splits in ((31, lens_a, 4), (32, lens_b, 4), (33, lens_a, 0)):
+        q, k, v = inputs.fmha_inputs(B, Hq, Hkv, 1, Skv, D, torch.float16, device=cuda_device, seed=seed)
+        expect = fmha.fmha_decode(q, k, v, kv_lens=lens, num_splits=splits)
+        got = torch.full_like(q, float("nan"))
+        rc = _call_static(L, q, k, v, got, lens, splits)
+        assert rc == 0, _lib.strerror(rc)
+        torch.cuda.synchronize()
+        assert not torch.isnan(got).any()
+        # same kernels, same split count: the results are expected to agree to the bit;
+        # the bound asserted is the 2e-3 max-abs tolerance the other decode tests use
+        assert float((got.float() - expect.float()).abs().max()) <= 2e-3
+        if splits:
+            assert torch.equal(got, expect)
+
+
+def test_static_scratch_rejects_what_does_not_fit(cuda_device):
+    from b200k import _lib, inputs
+    L = _lib.lib()
+    # 64 sequences x 32 heads x 64 splits x 130 floats = 68 MB of partials: beyond 16 MiB
+    q, k, v = inputs.fmha_inputs(64, 32, 8, 1, 128, 128, torch.float16, device=cuda_device, seed=1)
+    out = torch.zeros_like(q)
+    rc = _call_static(L, q, k, v, out, None, 64)
+    assert rc == -11 and "scratch" in _lib.strerror(rc)
+    assert torch.count_nonzero(out) == 0  # nothing was launched
+    # the same problem with the split count left to the library fits and runs
+    assert _call_static(L, q, k, v, out, None, 0) == 0
+    torch.cuda.synchronize()
+    from oracle import oracle
+    assert oracle.max_abs(out, oracle.fmha_ref(q, k, v)) <= 2e-3

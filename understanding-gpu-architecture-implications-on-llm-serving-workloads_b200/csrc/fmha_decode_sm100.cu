@@ -508,3 +508,103 @@ extern "C" int b200k_fmha_decode_splitkv(const void* Q, const void* K, const voi
   return bf16 ? B200K_DECODE(64, true) : B200K_DECODE(64, false);
 #undef B200K_DECODE
 }
+
+// ---------------------------------------------------------------------------
+// Variant for callers that cannot allocate device memory.
+//
+// Some hosts of this library must not call cudaMalloc on the path that runs the
+// kernel: an inference server whose memory pool was sized at start-up and that
+// treats any later driver allocation as a fault, a plugin loaded into a process
+// whose allocator it does not own, or code running between the steps of a
+// latency-critical loop where an allocation (which may synchronise the device)
+// is not acceptable.  For them the split-KV partial results live in the
+// file-scope array below instead of a caller-provided workspace.
+//
+// The array is part of the library image: every GPU that loads libb200k.so holds
+// kStaticScratchBytes of its memory until the process exits, whether or not this
+// entry point is ever called.  That is why its size is fixed and modest.
+// ---------------------------------------------------------------------------
+namespace b200k {
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(16) << 20;  // 16 MiB per GPU
+
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
+
+// Device address of g_decode_scratch on the current device.  In host code the
+// array's name is only a handle for the runtime, not an address a kernel could
+// use, so the address is asked for once per device, with that device current.
+int static_scratch_ptr(unsigned char** out) {
+  constexpr int kMaxDev = 64;
+  static unsigned char* ptrs[kMaxDev] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) {
+    (void)cudaGetLastError();
+    return B200K_ECUDA;
+  }
+  if (!ptrs[dev]) {
+    unsigned char* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_decode_scratch) != cudaSuccess || !p) {
+      (void)cudaGetLastError();
+      return B200K_ECUDA;
+    }
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return B200K_OK;
+}
+
+size_t decode_partials_bytes(int B, int Hq, int Hkv, int Sq, int D, int splits) {
+  const size_t rows = (size_t)B * Hkv * (size_t)(Hq / Hkv * Sq);
+  return rows * (size_t)splits * (size_t)(D + 2) * sizeof(float);
+}
+
+}  // namespace
+}  // namespace b200k
+
+extern "C" size_t b200k_fmha_decode_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int b200k_fmha_decode_splitkv_static(const void* Q, const void* K, const void* V, void* O, int B, int Hq,
+                                                int Hkv, int Sq, int Skv, int D, const int64_t q_strides[3],
+                                                const int64_t k_strides[3], const int64_t v_strides[3],
+                                                const int64_t o_strides[3], float scale, const int32_t* kv_lens,
+                                                int num_splits, int dtype, b200k_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (dtype != B200K_F16 && dtype != B200K_BF16) return B200K_EDTYPE;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0 || Hq % Hkv != 0) return B200K_ESHAPE;
+  if (D != 64 && D != 128) return B200K_EHEADDIM;
+  if (Hq / Hkv * Sq > kMaxRows) return B200K_ESHAPE;
+  if (!Q || !K || !V || !O || !q_strides || !k_strides || !v_strides || !o_strides) return B200K_EARG;
+  if (!(scale > 0.f) || num_splits < 0 || num_splits > 1024) return B200K_EARG;
+  auto ok16 = [](const void* ptr, const int64_t* st) {
+    return aligned16(ptr) && st[0] % 8 == 0 && st[1] % 8 == 0 && st[2] % 8 == 0;
+  };
+  if (!ok16(K, k_strides) || !ok16(V, v_strides)) return B200K_EALIGN;
+  if ((reinterpret_cast<uintptr_t>(Q) & 3) || q_strides[0] % 2 || q_strides[1] % 2 || q_strides[2] % 2)
+    return B200K_EALIGN;
+  if (!b200k_device_supported()) return B200K_ENOGPU;
+  // An explicit split count must fit the fixed scratch; with 0 the library's usual choice is
+  // lowered until it fits.  A problem that does not fit even unsplit is refused.
+  int splits = num_splits;
+  if (splits == 0) {
+    splits = choose_splits(B, Hkv, Skv);
+    while (splits > 1 && decode_partials_bytes(B, Hq, Hkv, Sq, D, splits) > kStaticScratchBytes) --splits;
+  }
+  if (decode_partials_bytes(B, Hq, Hkv, Sq, D, splits) > kStaticScratchBytes) return B200K_ESCRATCH;
+  unsigned char* scratch = nullptr;
+  int r = static_scratch_ptr(&scratch);
+  if (r) return r;
+  const size_t rows = (size_t)B * Hkv * (size_t)(Hq / Hkv * Sq);
+  // Nothing has to start at zero: every (max, sum, partial O) slot the reduction kernel
+  // reads was written by the split kernel of this same call; slots of splits past a
+  // sequence's length are neither written nor read.
+  float* part_o = reinterpret_cast<float*>(scratch);
+  float* part_ml = part_o + rows * splits * D;
+  const bool bf16 = dtype == B200K_BF16;
+#define B200K_DECODE(DD, BF)                                                                                     \
+  launch_decode<DD, BF>(Q, K, V, O, B, Hq, Hkv, Sq, Skv, q_strides, k_strides, v_strides, o_strides, scale, kv_lens, \
+                        splits, part_o, part_ml, stream)
+  if (D == 128) return bf16 ? B200K_DECODE(128, true) : B200K_DECODE(128, false);
+  return bf16 ? B200K_DECODE(64, true) : B200K_DECODE(64, false);
+#undef B200K_DECODE
+}

@@ -120,6 +120,7 @@ const char* b200k_strerror(int code) {
     case B200K_ETMAP: return "tensor map encoding failed";
     case B200K_EARG: return "invalid argument";
     case B200K_ENOGPU: return "no sm_100 device is current";
+    case B200K_ESCRATCH: return "problem does not fit the library's built-in scratch array";
     default: return "unknown b200k error";
   }
 }
