@@ -27,7 +27,7 @@ def _inputs(M, N, K, dtype, seed=0, std_b=1.0):
     return a, b
 
 
-@pytest.mark.parametrize("variant", [1, 4])
+@pytest.mark.parametrize("variant", [1, 2, 4])
 def test_structured_identity(cuda_device, variant):
     """A = I picks rows of B; B = I picks columns of A: catches operand-layout
     (descriptor / swizzle / major-ness) mistakes exactly, with no tolerance."""
@@ -46,7 +46,7 @@ def test_structured_identity(cuda_device, variant):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("variant", [0, 1, 4, 5])
+@pytest.mark.parametrize("variant", [0, 1, 2, 4, 5])
 @pytest.mark.parametrize("shape", [(128, 256, 64), (128, 128, 128), (256, 512, 256), (1024, 1024, 1024),
                                    (384, 768, 4096)])
 def test_parity_aligned(cuda_device, shape, variant, dtype):
@@ -57,7 +57,7 @@ def test_parity_aligned(cuda_device, shape, variant, dtype):
     assert err <= TOL, err
 
 
-@pytest.mark.parametrize("variant", [0, 1, 4])
+@pytest.mark.parametrize("variant", [0, 1, 2, 4])
 @pytest.mark.parametrize("shape", [(1, 8, 8), (7, 72, 40), (63, 136, 72), (65, 264, 200), (129, 520, 1000),
                                    (16, 4096, 4096), (300, 11008, 136)])
 def test_parity_ragged_edges(cuda_device, shape, variant):
@@ -91,7 +91,7 @@ def test_config1_fp16_1024(cuda_device):
     import gemm_unified
     a, b = inputs.gemm_c1()
     ref = oracle.gemm_ref(a, b)
-    for idx in (0, 8, 9, 10, 12):
+    for idx in (0, 8, 9, 10, 11, 12):
         c = gemm_unified.ops.fine_gemm(a.to(cuda_device), b.to(cuda_device), idx)
         assert c.dtype == torch.float16 and c.shape == (1024, 1024)
         err = oracle.rel_frobenius(c, ref)

@@ -10,6 +10,8 @@
 //               overlapping the next tile's main loop
 // Ragged M, N, K edges are handled by TMA: loads outside the tensor read zero,
 // stores outside are clipped.
+// The same kernel also runs as a CTA pair (cluster of 2, tcgen05 cta_group::2) on 256 x 256
+// tiles: each CTA stages its own half of the operands, the leader issues the MMAs for both.
 //
 // Reference contract: kernels/gemm/pkg/gemm_unified/csrc/auto/gemm_0.cu:12-20
 // (a[i*K+k], b[k*N+j], c[i*N+j]); reference launchers e.g.
@@ -52,22 +54,29 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
 }
 
-template <int BN, int STAGES>
+// CTAS = 1: one CTA per 128 x BN tile.  CTAS = 2: a CTA pair (cluster of 2, cta_group::2) per
+// 256 x BN tile; each CTA loads its own 128 rows of A and its own BN/2 columns of B, the pair
+// leader issues one M = 256 MMA that reads both CTAs' shared memory and writes 128 accumulator
+// rows into each CTA's TMEM, so every B element is staged once per 256 rows instead of per 128.
+template <int CTAS, int BN, int STAGES>
 struct GemmSmem {
+  static constexpr uint32_t kBnLocal = BN / CTAS;  // B columns staged by one CTA
   static constexpr uint32_t kABytes = kBM * kBK * 2;
-  static constexpr uint32_t kBBytes = BN * kBK * 2;
+  static constexpr uint32_t kBBytes = kBnLocal * kBK * 2;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kStagingBytes = 4 * 2 * 4096;  // 4 epilogue warps x 2 buffers x (32 rows x 128 B)
   static constexpr uint32_t kBarOffset = STAGES * kStageBytes + kStagingBytes;
   static constexpr uint32_t kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
 };
 
-template <int BN, int STAGES, bool BF16>
+template <int CTAS, int BN, int STAGES, bool BF16>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_1cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int* status) {
-  using L = GemmSmem<BN, STAGES>;
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int* status) {
+  using L = GemmSmem<CTAS, BN, STAGES>;
   constexpr uint32_t kTmemCols = 2 * BN;
+  constexpr int kTileM = kBM * CTAS;
+  constexpr int kKid = CTAS == 1 ? KID_GEMM : KID_GEMM2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = smem + STAGES * L::kStageBytes;
@@ -79,7 +88,10 @@ gemm_1cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_m = (M + kBM - 1) / kBM;
+  const uint32_t rank = CTAS == 1 ? 0u : cluster_ctarank();  // 0 = pair leader
+  const int unit = blockIdx.x / CTAS;                       // CTA (or CTA pair) index
+  const int num_units = gridDim.x / CTAS;
+  const int num_m = (M + kTileM - 1) / kTileM;
   const int num_n = (N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (K + kBK - 1) / kBK;
@@ -91,7 +103,7 @@ gemm_1cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 4);
+      mbar_init(&tmem_empty[a], 4 * CTAS);
     }
     fence_mbar_init();
     prefetch_tmap(&tmA);
@@ -99,11 +111,12 @@ gemm_1cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     prefetch_tmap(&tmC);
   }
   if (warp == 1) {
-    tmem_alloc<1>(tmem_holder, kTmemCols);
-    tmem_relinquish<1>();
+    tmem_alloc<CTAS>(tmem_holder, kTmemCols);
+    tmem_relinquish<CTAS>();
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CTAS == 2) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
@@ -112,22 +125,34 @@ gemm_1cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (elect_one()) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < num_tiles && ok; t += num_units) {
         int mb, nb;
         tile_coords(t, num_m, num_n, mb, nb);
+        const int row0 = mb * kTileM + (int)rank * kBM;
+        const int col0 = nb * BN + (int)rank * (int)L::kBnLocal;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
-            report_timeout(status, KID_GEMM, ROLE_PRODUCER);
+            report_timeout(status, kKid, ROLE_PRODUCER);
             ok = false;
             break;
           }
           uint8_t* sa = smem + stage * L::kStageBytes;
           uint8_t* sb = sa + L::kABytes;
-          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
-          tma_load_2d(sa, &tmA, &full_bar[stage], kb * kBK, mb * kBM);
+          if constexpr (CTAS == 1) {
+            mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+            tma_load_2d(sa, &tmA, &full_bar[stage], kb * kBK, row0);
 #pragma unroll
-          for (int j = 0; j < BN / 64; ++j)
-            tma_load_2d(sb + j * (kBK * 128), &tmB, &full_bar[stage], nb * BN + j * 64, kb * kBK);
+            for (int j = 0; j < (int)L::kBnLocal / 64; ++j)
+              tma_load_2d(sb + j * (kBK * 128), &tmB, &full_bar[stage], col0 + j * 64, kb * kBK);
+          } else {
+            // both CTAs' bytes are counted on the leader's barrier, which the MMA thread waits on
+            if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * L::kStageBytes);
+            const uint32_t bar = map_to_cta(&full_bar[stage], 0);
+            tma_load_2d_pair(smem_u32(sa), &tmA, bar, kb * kBK, row0);
+#pragma unroll
+            for (int j = 0; j < (int)L::kBnLocal / 64; ++j)
+              tma_load_2d_pair(smem_u32(sb + j * (kBK * 128)), &tmB, bar, col0 + j * 64, kb * kBK);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -136,24 +161,24 @@ gemm_1cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    // ------------------------------- MMA issuer -------------------------------
-    if (elect_one()) {
-      constexpr uint32_t idesc = make_idesc_f16(BF16 ? 1 : 0, /*a K-major*/ 0, /*b MN-major*/ 1, kBM, BN);
+    // ------------------------- MMA issuer (pair leader only) -------------------------
+    if (rank == 0 && elect_one()) {
+      constexpr uint32_t idesc = make_idesc_f16(BF16 ? 1 : 0, /*a K-major*/ 0, /*b MN-major*/ 1, kTileM, BN);
       uint32_t stage = 0, phase = 0;
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      for (int t = unit; t < num_tiles && ok; t += num_units, ++it) {
         const uint32_t acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) {
-          report_timeout(status, KID_GEMM, ROLE_MMA);
+          report_timeout(status, kKid, ROLE_MMA);
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase)) {
-            report_timeout(status, KID_GEMM, ROLE_MMA);
+            report_timeout(status, kKid, ROLE_MMA);
             ok = false;
             break;
           }
@@ -168,16 +193,20 @@ gemm_1cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
             // advance 16 k: A by 32 B inside the swizzled row, B by 16 rows of 128 B
-            umma_ss<1>(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), idesc,
-                       (kb > 0 || k > 0) ? 1u : 0u);
+            umma_ss<CTAS>(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), idesc,
+                          (kb > 0 || k > 0) ? 1u : 0u);
           }
-          umma_commit<1>(&empty_bar[stage]);
+          umma_commit<CTAS>(&empty_bar[stage]);
+          if constexpr (CTAS == 2) umma_commit_2cta_to(&empty_bar[stage], 1);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) umma_commit<1>(&tmem_full[acc]);
+        if (ok) {
+          umma_commit<CTAS>(&tmem_full[acc]);
+          if constexpr (CTAS == 2) umma_commit_2cta_to(&tmem_full[acc], 1);
+        }
       }
     }
   } else {
@@ -186,18 +215,18 @@ gemm_1cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint8_t* stg = staging + ew * 8192;
     uint32_t it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+    for (int t = unit; t < num_tiles && ok; t += num_units, ++it) {
       int mb, nb;
       tile_coords(t, num_m, num_n, mb, nb);
       const uint32_t acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tmem_full[acc], acc_phase)) {
-        if (lane == 0) report_timeout(status, KID_GEMM, ROLE_EPILOGUE);
+        if (lane == 0) report_timeout(status, kKid, ROLE_EPILOGUE);
         ok = false;
         break;
       }
       tc_fence_after();
-      const int row0 = mb * kBM + ew * 32;
+      const int row0 = mb * kTileM + (int)rank * kBM + ew * 32;
 #pragma unroll 1
       for (int c = 0; c < BN / 64; ++c) {
         uint32_t v[32], w[32];
@@ -237,16 +266,22 @@ gemm_1cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (lane == 0) {
+        if constexpr (CTAS == 1)
+          mbar_arrive(&tmem_empty[acc]);
+        else
+          mbar_arrive_cluster(&tmem_empty[acc], 0);  // the leader's MMA thread waits for both CTAs
+      }
     }
     if (lane == 0) tma_store_wait_all<0>();
   }
 
   tc_fence_before();
   __syncthreads();
+  if constexpr (CTAS == 2) cluster_sync_all();  // the leader may still read this CTA's operands until here
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc<1>(tmem_base, kTmemCols);
+    tmem_dealloc<CTAS>(tmem_base, kTmemCols);
   }
 }
 
@@ -314,11 +349,11 @@ gemm_generic_kernel(const void* __restrict__ A, const void* __restrict__ B, void
   }
 }
 
-template <int BN, int STAGES, bool BF16>
-int launch_1cta(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
-                cudaStream_t stream) {
-  using L = GemmSmem<BN, STAGES>;
-  auto kfn = gemm_1cta_kernel<BN, STAGES, BF16>;
+template <int CTAS, int BN, int STAGES, bool BF16>
+int launch_tc(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+              cudaStream_t stream) {
+  using L = GemmSmem<CTAS, BN, STAGES>;
+  auto kfn = gemm_tc_kernel<CTAS, BN, STAGES, BF16>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -353,11 +388,27 @@ int launch_1cta(const void* A, const void* B, void* C, int M, int N, int K, int6
   }
   int* status = status_ptr();
   if (!status) return B200K_ECUDA;
-  const int num_tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
+  const int num_tiles = ((M + kBM * CTAS - 1) / (kBM * CTAS)) * ((N + BN - 1) / BN);
   const int sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
-  const int grid = num_tiles < sms ? num_tiles : sms;
-  kfn<<<grid, kGemmThreads, L::kTotal, stream>>>(tmA, tmB, tmC, M, N, K, status);
+  const int units = num_tiles < sms / CTAS ? num_tiles : sms / CTAS;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(units * CTAS));
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = L::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kfn, tmA, tmB, tmC, M, N, K, status);
   count_launch();
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return B200K_ECUDA;
+  }
   return check_launch();
 }
 
@@ -407,15 +458,18 @@ extern "C" int b200k_gemm(const void* A, const void* B, void* C, int M, int N, i
   const bool bf16 = dtype == B200K_BF16;
   switch (variant) {
     case B200K_GEMM_1CTA:
-    case B200K_GEMM_2CTA:
     case B200K_GEMM_SKINNY:
       if (!tma_ok) return B200K_EALIGN;
-      return bf16 ? launch_1cta<256, 4, true>(A, B, C, M, N, K, lda, ldb, ldc, stream)
-                  : launch_1cta<256, 4, false>(A, B, C, M, N, K, lda, ldb, ldc, stream);
+      return bf16 ? launch_tc<1, 256, 4, true>(A, B, C, M, N, K, lda, ldb, ldc, stream)
+                  : launch_tc<1, 256, 4, false>(A, B, C, M, N, K, lda, ldb, ldc, stream);
+    case B200K_GEMM_2CTA:
+      if (!tma_ok) return B200K_EALIGN;
+      return bf16 ? launch_tc<2, 256, 6, true>(A, B, C, M, N, K, lda, ldb, ldc, stream)
+                  : launch_tc<2, 256, 6, false>(A, B, C, M, N, K, lda, ldb, ldc, stream);
     case B200K_GEMM_1CTA_N128:
       if (!tma_ok) return B200K_EALIGN;
-      return bf16 ? launch_1cta<128, 6, true>(A, B, C, M, N, K, lda, ldb, ldc, stream)
-                  : launch_1cta<128, 6, false>(A, B, C, M, N, K, lda, ldb, ldc, stream);
+      return bf16 ? launch_tc<1, 128, 6, true>(A, B, C, M, N, K, lda, ldb, ldc, stream)
+                  : launch_tc<1, 128, 6, false>(A, B, C, M, N, K, lda, ldb, ldc, stream);
     case B200K_GEMM_GENERIC:
       return bf16 ? launch_generic<true>(A, B, C, M, N, K, lda, ldb, ldc, stream)
                   : launch_generic<false>(A, B, C, M, N, K, lda, ldb, ldc, stream);

@@ -11,7 +11,7 @@
 namespace b200k {
 
 // ---------------------------------------------------------------------------
-// device status word (one int4 per device, owned by status.cu)
+// device status word (one int[4] per device, owned by host_common.cu)
 // ---------------------------------------------------------------------------
 enum : int { KID_GEMM = 1, KID_GEMM2 = 2, KID_FMHA = 3, KID_DECODE = 4 };
 enum : int { ROLE_PRODUCER = 1, ROLE_MMA = 2, ROLE_EPILOGUE = 3, ROLE_SOFTMAX = 4, ROLE_CORRECTION = 5 };
@@ -42,6 +42,25 @@ __device__ __forceinline__ bool elect_one() {
 
 __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// thread-block cluster
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `p` (a pointer into this CTA's shared memory) as seen in CTA `cta`
+__device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t cta) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(p)), "r"(cta));
+  return remote;
 }
 
 // ---------------------------------------------------------------------------
@@ -114,12 +133,14 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* m, uin
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
-// variant taking raw shared addresses (used to signal a peer CTA's barrier in a CTA pair)
-__device__ __forceinline__ void tma_load_2d_raw(uint32_t dst, const CUtensorMap* m, uint32_t bar, int x, int y) {
+// CTA-pair form: the data lands in the issuing CTA's shared memory, the completion bytes are
+// signalled on `bar_cluster_addr`, a shared::cluster address that may name the pair leader's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int x,
+                                                 int y) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y)
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y)
       : "memory");
 }
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z,
