@@ -112,6 +112,30 @@ def test_config2_llm_shapes_rows(cuda_device, M, dtype):
         assert err <= TOL, (M, K, N, err)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 128, 64), (16, 256, 4096), (64, 4096, 4096), (128, 1000, 2048), (7, 136, 200),
+                                   (33, 11008, 4096), (100, 520, 11008)])
+def test_skinny_split_k_clusters(cuda_device, shape, dtype):
+    """M <= 128: split-K inside clusters of 1..8 CTAs with the reduction through distributed
+    shared memory; ragged N and K; bit-identical reruns (fixed summation order)."""
+    M, N, K = shape
+    a, b = _inputs(M, N, K, dtype, seed=M + N + K, std_b=0.05)
+    c1 = _run(a, b, 3, cuda_device)
+    c2 = _run(a, b, 3, cuda_device)
+    assert torch.equal(c1, c2)
+    err = oracle.rel_frobenius(c1, oracle.gemm_ref(a, b))
+    assert err <= TOL, err
+
+
+def test_skinny_rejects_large_m(cuda_device):
+    from b200k import _lib, gemm
+    a = torch.zeros(256, 64, dtype=torch.float16, device=cuda_device)
+    b = torch.zeros(64, 128, dtype=torch.float16, device=cuda_device)
+    with pytest.raises(_lib.B200KError) as e:
+        gemm.gemm(a, b, variant=3)
+    assert e.value.code == -2
+
+
 def test_determinism(cuda_device):
     a, b = _inputs(512, 1024, 2048, torch.bfloat16, seed=3)
     outs = [_run(a, b, 1, cuda_device) for _ in range(3)]

@@ -1,0 +1,341 @@
+// Skinny GEMM (M <= 128 rows of activations against a large weight): bound by streaming the
+// weight B[K,N] from HBM once, so the design goal is CTAs and weight bytes in flight, not MMA
+// efficiency.
+//
+//   * Operands are swapped for the tensor core: the 128 weight columns of a slab are the MMA's
+//     M rows (A operand, MN-major because B[K,N] is contiguous along N) and the activation rows
+//     are the MMA's N columns (B operand, K-major), padded only to MPAD in {16, 32, 64, 128}.
+//     A stage is 32 KB of weights (256 columns: 512 contiguous bytes of every k-row, which
+//     keeps DRAM pages open longer than 128-byte pieces) plus MPAD*128 bytes of activations,
+//     so small M leaves room for more weight bytes in flight (6 stages at M <= 16).
+//   * One 256-column slab of B per cluster of S CTAs (S in 1..8, about 96 CTAs in all);
+//     CTA r of the cluster streams k-blocks [r*nkb/S, (r+1)*nkb/S): split-K in a cluster.
+//   * Roles per CTA: a TMA warp, one MMA thread (two tcgen05.mma M = 128, N = MPAD, K = 16 per
+//     k-step, accumulators D[weight column][activation row] in 2 x MPAD TMEM columns), four
+//     warps that drain.
+//   * The split-K partials never go to HBM: every CTA writes its fp32 partial tile [row][256]
+//     to its own shared memory (the drained stage buffers), the cluster synchronises, and CTA r
+//     sums its share of the columns of all S tiles through distributed shared memory in rank
+//     order 0..S-1 (bit-identical from run to run), converts and stores its part of C.
+//
+// Reference contract: kernels/gemm/pkg/gemm_unified/csrc/auto/gemm_0.cu:12-20.  The
+// reference's tensor-core rungs cannot run these shapes at all (no bounds checks, M % 128
+// required: kernels/gemm/pkg/gemm_unified/csrc/semi/gemm_11_nv.cu:179-199).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <stdlib.h>
+
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace b200k {
+namespace {
+
+constexpr int kSkBK = 64, kSkThreads = 192;
+constexpr int kSkBN = 256;                        // weight columns per CTA: 512 contiguous bytes per k-row
+constexpr int kSkSub = kSkBN / 128;               // MMAs of 128 weight columns each
+constexpr uint32_t kSkWBytes = kSkBN * kSkBK * 2;  // weight tile of one stage (32 KB)
+
+template <int MPAD>
+struct SkinnySmem {
+  static constexpr uint32_t kXBytes = MPAD * kSkBK * 2;  // activation tile of one stage
+  static constexpr uint32_t kStageBytes = kSkWBytes + (kXBytes < 1024 ? 1024 : kXBytes);
+  // one CTA per SM: as many stages as fit in ~208 KB, at most 6
+  static constexpr int kStages = (208 * 1024 / kStageBytes) > 6 ? 6 : (208 * 1024 / kStageBytes);
+  static constexpr uint32_t kTileBytes = MPAD * kSkBN * 4;  // fp32 partial tile, reuses the stage buffers
+  static constexpr uint32_t kBarOff = kStages * kStageBytes > kTileBytes ? kStages * kStageBytes : kTileBytes;
+  static constexpr uint32_t kTotal = kBarOff + 128 + 1024;
+};
+
+__device__ __forceinline__ uint32_t cluster_size_x() {
+  uint32_t n;
+  asm volatile("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(n));
+  return n;
+}
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2s(float lo, float hi) {
+  if constexpr (BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+template <int MPAD, bool BF16>
+__global__ void __launch_bounds__(kSkThreads, 1)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
+                   uint16_t* __restrict__ C, int64_t ldc, int M, int N, int K, int* status) {
+  using L = SkinnySmem<MPAD>;
+  constexpr int kStages = L::kStages;
+  constexpr uint32_t kAccCols = MPAD < 32 ? 32 : MPAD;  // TMEM columns of one accumulator
+  constexpr uint32_t kTmemCols = kSkSub * kAccCols;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full = empty_bar + kStages;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_full + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t S = cluster_size_x();
+  const uint32_t rank = cluster_ctarank();
+  const int n0 = (blockIdx.x / S) * kSkBN;
+  const int num_kb = (K + kSkBK - 1) / kSkBK;
+  const int kb_begin = (int)((int64_t)rank * num_kb / S);
+  const int kb_end = (int)((int64_t)(rank + 1) * num_kb / S);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tmem_full, 1);
+    fence_mbar_init();
+    prefetch_tmap(&tmX);
+    prefetch_tmap(&tmW);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(tmem_holder, kTmemCols);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      uint32_t stage = 0, phase = 0;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+          report_timeout(status, KID_GEMM, ROLE_PRODUCER);
+          break;
+        }
+        uint8_t* sw = smem + stage * L::kStageBytes;
+        uint8_t* sx = sw + kSkWBytes;
+        mbar_expect_tx(&full_bar[stage], kSkWBytes + L::kXBytes);
+#pragma unroll
+        for (int j = 0; j < kSkBN / 64; ++j)
+          tma_load_2d(sw + j * (kSkBK * 128), &tmW, &full_bar[stage], n0 + j * 64, kb * kSkBK);
+        tma_load_2d(sx, &tmX, &full_bar[stage], kb * kSkBK, 0);
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      // A = weights, MN-major (64 weight columns per 128-byte row, 8 k-rows per 1024-byte group,
+      // second 64-column box kSkBK*128 bytes further); B = activations, K-major.
+      constexpr uint32_t idesc = make_idesc_f16(BF16 ? 1 : 0, /*a MN-major*/ 1, /*b K-major*/ 0, 128, MPAD);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait(&full_bar[stage], phase)) {
+          report_timeout(status, KID_GEMM, ROLE_MMA);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t w_addr = smem_u32(smem + stage * L::kStageBytes);
+        const uint64_t xdesc = make_smem_desc_sw128(w_addr + kSkWBytes, 16, 1024);
+#pragma unroll
+        for (int sub = 0; sub < kSkSub; ++sub) {
+          // weight columns [128*sub, 128*sub+128): two 64-column boxes
+          const uint64_t wdesc = make_smem_desc_sw128(w_addr + sub * 2 * (kSkBK * 128), kSkBK * 128, 1024);
+#pragma unroll
+          for (int k = 0; k < kSkBK / 16; ++k)
+            umma_ss<1>(tmem_base + sub * kAccCols, wdesc + (uint64_t)(k * 128), xdesc + (uint64_t)(k * 2), idesc,
+                       (kb > kb_begin || k > 0) ? 1u : 0u);
+        }
+        umma_commit<1>(&empty_bar[stage]);
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok) umma_commit<1>(tmem_full);
+    }
+  } else {
+    // drain TMEM (lane = weight column, TMEM column = activation row) into this CTA's fp32
+    // tile [row][kSkBN]: consecutive lanes write consecutive words
+    const int ew = warp & 3;
+    const bool have = kb_end > kb_begin;
+    bool ok = true;
+    if (have && !mbar_wait(tmem_full, 0)) {
+      if (lane == 0) report_timeout(status, KID_GEMM, ROLE_EPILOGUE);
+      ok = false;
+    }
+    tc_fence_after();
+    float* tile = reinterpret_cast<float*>(smem);
+    constexpr int kChunk = MPAD < 32 ? 16 : 32;
+#pragma unroll 1
+    for (int sub = 0; sub < kSkSub; ++sub) {
+      const int n = sub * 128 + ew * 32 + lane;
+#pragma unroll 1
+      for (int cb = 0; cb < MPAD / kChunk; ++cb) {
+        if (cb * kChunk >= M) break;
+        uint32_t v[kChunk];
+        if (have && ok) {
+          const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + sub * kAccCols + cb * kChunk;
+          if constexpr (kChunk == 16)
+            tmem_ld16(taddr, v);
+          else
+            tmem_ld32(taddr, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < kChunk; ++e) v[e] = 0u;
+        }
+#pragma unroll
+        for (int e = 0; e < kChunk; ++e) {
+          const int m = cb * kChunk + e;
+          if (m < M) tile[m * kSkBN + n] = __uint_as_float(v[e]);
+        }
+      }
+    }
+  }
+
+  // every CTA's partial tile is complete and visible to the cluster
+  tc_fence_before();
+  cluster_sync_all();
+
+  {
+    // this CTA's slice of the tile's 16-byte chunks (any S in 1..8 divides them unevenly at most by one)
+    const int c_begin = (int)rank * (kSkBN / 4) / (int)S;
+    const int c_end = ((int)rank + 1) * (kSkBN / 4) / (int)S;
+    const int w4 = c_end - c_begin;
+    const int items = M * w4;
+    const uint32_t tile_addr = smem_u32(smem);
+    for (int item = threadIdx.x; item < items; item += kSkThreads) {
+      const int row = item / w4;
+      const int c = c_begin + item % w4;
+      const int n = n0 + c * 4;
+      if (n >= N) continue;
+      const uint32_t off = (uint32_t)(row * kSkBN + c * 4) * 4u;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (uint32_t s = 0; s < S; ++s) {
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(tile_addr + off), "r"(s));
+        const float4 v = ld_dsmem_f4(remote);
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
+      }
+      uint2 o;
+      o.x = pack2s<BF16>(acc.x, acc.y);
+      o.y = pack2s<BF16>(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(C + (int64_t)row * ldc + n) = o;
+    }
+  }
+
+  // nobody leaves while a peer may still read its tile
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+
+// Cluster size (K-splits per column slab).  Measured on B200: the rate peaks near 96 CTAs in
+// flight (more splits add distributed-shared-memory reduction traffic faster than they add
+// bytes in flight), so S = round(96 / slabs), at most 8.  B200K_SKINNY_S overrides it.
+int skinny_cluster_size(int N, int K) {
+  const int tiles = (N + kSkBN - 1) / kSkBN;
+  const int num_kb = (K + kSkBK - 1) / kSkBK;
+  int s = (96 + tiles / 2) / tiles;
+  if (s > 8) s = 8;
+  if (s > num_kb / 2) s = num_kb / 2;
+  if (s < 1) s = 1;
+  if (const char* e = getenv("B200K_SKINNY_S")) {
+    const int v = atoi(e);
+    if (v >= 1 && v <= 8 && v <= num_kb) s = v;
+  }
+  return s;
+}
+
+template <int MPAD, bool BF16>
+static int launch_skinny_t(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                           int64_t ldc, cudaStream_t stream) {
+  using L = SkinnySmem<MPAD>;
+  auto kfn = gemm_skinny_kernel<MPAD, BF16>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev & 63]) {
+    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return B200K_ECUDA;
+    }
+    configured[dev & 63] = true;
+  }
+  CUtensorMap tmX, tmW;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {kSkBK, (uint32_t)MPAD};
+    int r = encode_tmap_16bit(&tmX, A, 2, dims, str, box, true);
+    if (r) return r;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
+    uint64_t str[1] = {(uint64_t)ldb * 2};
+    uint32_t box[2] = {64, kSkBK};
+    int r = encode_tmap_16bit(&tmW, B, 2, dims, str, box, true);
+    if (r) return r;
+  }
+  int* status = status_ptr();
+  if (!status) return B200K_ECUDA;
+  const int S = skinny_cluster_size(N, K);
+  const int tiles = (N + kSkBN - 1) / kSkBN;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(tiles * S));
+  cfg.blockDim = dim3(kSkThreads);
+  cfg.dynamicSmemBytes = L::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)S;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kfn, tmX, tmW, reinterpret_cast<uint16_t*>(C), ldc, M, N, K, status);
+  count_launch();
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return B200K_ECUDA;
+  }
+  return check_launch();
+}
+
+int launch_skinny(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                  bool bf16, cudaStream_t stream) {
+  if (M > 128) return B200K_ESHAPE;
+#define B200K_SKINNY(MP)                                                                       \
+  return bf16 ? launch_skinny_t<MP, true>(A, B, C, M, N, K, lda, ldb, ldc, stream)              \
+              : launch_skinny_t<MP, false>(A, B, C, M, N, K, lda, ldb, ldc, stream)
+  if (M <= 16) { B200K_SKINNY(16); }
+  if (M <= 32) { B200K_SKINNY(32); }
+  if (M <= 64) { B200K_SKINNY(64); }
+  B200K_SKINNY(128);
+#undef B200K_SKINNY
+}
+
+}  // namespace b200k

@@ -451,14 +451,24 @@ extern "C" int b200k_gemm(const void* A, const void* B, void* C, int M, int N, i
       variant = B200K_GEMM_GENERIC;
     } else {
       const int sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
+      const long pair_tiles = (long)((M + 255) / 256) * ((N + 255) / 256);
       const long tiles256 = (long)((M + 127) / 128) * ((N + 255) / 256);
-      variant = tiles256 >= sms ? B200K_GEMM_1CTA : B200K_GEMM_1CTA_N128;
+      if (M <= 32 || (M <= 128 && (N + 127) / 128 < 64))
+        variant = B200K_GEMM_SKINNY;  // weight streaming, split-K inside clusters
+      else if (M <= 128)
+        variant = B200K_GEMM_1CTA_N128;  // wide weights: enough 128-column tiles without split-K
+      else if (pair_tiles >= sms / 2)
+        variant = B200K_GEMM_2CTA;  // at least one full wave of 256x256 pair tiles
+      else
+        variant = tiles256 >= sms ? B200K_GEMM_1CTA : B200K_GEMM_1CTA_N128;
     }
   }
   const bool bf16 = dtype == B200K_BF16;
   switch (variant) {
-    case B200K_GEMM_1CTA:
     case B200K_GEMM_SKINNY:
+      if (!tma_ok) return B200K_EALIGN;
+      return launch_skinny(A, B, C, M, N, K, lda, ldb, ldc, bf16, stream);
+    case B200K_GEMM_1CTA:
       if (!tma_ok) return B200K_EALIGN;
       return bf16 ? launch_tc<1, 256, 4, true>(A, B, C, M, N, K, lda, ldb, ldc, stream)
                   : launch_tc<1, 256, 4, false>(A, B, C, M, N, K, lda, ldb, ldc, stream);

@@ -33,6 +33,10 @@ struct DevInfo {
 };
 const DevInfo& dev_info();
 
+// Skinny GEMM (M <= 128): split-K inside thread-block clusters (gemm_skinny_sm100.cu).
+int launch_skinny(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                  bool bf16, cudaStream_t stream);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace b200k
