@@ -6,6 +6,8 @@
 //   warps 0-3   softmax group of tile 0 (thread = query row = TMEM lane)
 //   warps 4-7   softmax group of tile 1
 //   warp  8     TMA loader: Q tiles once, K and V blocks through 2-deep rings
+//   warps 10-11 idle (they complete the third warpgroup so that it can hand most of its
+//               registers to the softmax warpgroups with setmaxnreg: 56 vs 224 per thread)
 //   warp  9     MMA issuer: S_i = Q_i K_j^T (both operands K-major) into TMEM, then
 //               O_i += P_i V_j with P_i read from TMEM and V_j as an MN-major
 //               shared-memory operand (V is [kv, d] with d contiguous)
@@ -30,7 +32,7 @@
 namespace b200k {
 namespace {
 
-constexpr int kFmhaThreads = 320;
+constexpr int kFmhaThreads = 384;  // 2 softmax warpgroups + 1 warpgroup holding the TMA and MMA warps
 constexpr int kTile = 128;  // query rows per tile and keys per block
 constexpr float kRescaleThreshold = 8.0f;
 
@@ -58,6 +60,44 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// packed fp32 pairs (one instruction for two lanes of a row)
+__device__ __forceinline__ uint64_t f2pack(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void f2unpack(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 template <bool BF16>
@@ -146,8 +186,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 8) {
+  if (warp >= 10) {
+    // idle warps of the third warpgroup
+    reg_dealloc<56>();
+  } else if (warp == 8) {
     // ------------------------------- TMA loader -------------------------------
+    reg_dealloc<56>();
     if (elect_one() && nb_max > 0) {
       auto load_tile = [&](const CUtensorMap* tm, uint8_t* dst, uint64_t* bar, int row, int head) {
         mbar_expect_tx(bar, L::kTileBytes);
@@ -179,6 +223,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (warp == 9) {
     // ------------------------------- MMA issuer -------------------------------
+    reg_dealloc<56>();
     if (elect_one() && nb_max > 0) {
       constexpr uint32_t idesc_s = make_idesc_f16(BF16 ? 1 : 0, 0, 0, kTile, kTile);
       constexpr uint32_t idesc_pv = make_idesc_f16(BF16 ? 1 : 0, 0, 1, kTile, D);
@@ -265,6 +310,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else {
     // ----------------------------- softmax groups -----------------------------
+    reg_alloc<224>();
     const int i = warp >> 2;             // tile of this group
     const int row = threadIdx.x & 127;   // query row inside the tile = TMEM lane
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
@@ -302,11 +348,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int k = 0; k < 128; k += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(s[k + 0]));
-          mx1 = fmaxf(mx1, __uint_as_float(s[k + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(s[k + 2]));
-          mx3 = fmaxf(mx3, __uint_as_float(s[k + 3]));
+        for (int k = 0; k < 128; k += 8) {
+          mx0 = max3(mx0, __uint_as_float(s[k + 0]), __uint_as_float(s[k + 1]));
+          mx1 = max3(mx1, __uint_as_float(s[k + 2]), __uint_as_float(s[k + 3]));
+          mx2 = max3(mx2, __uint_as_float(s[k + 4]), __uint_as_float(s[k + 5]));
+          mx3 = max3(mx3, __uint_as_float(s[k + 6]), __uint_as_float(s[k + 7]));
         }
         const float m_new = fmaxf(m_use, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc);
         if (j == 0) {
@@ -322,28 +368,33 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               uint32_t o[32];
               tmem_ld32(o_tmem + c * 32, o);
               tmem_ld_wait();
+              const uint64_t f2 = f2pack(f, f);
 #pragma unroll
-              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
+              for (int e = 0; e < 32; e += 2) {
+                float a, b;
+                f2unpack(mul2(f2pack(__uint_as_float(o[e]), __uint_as_float(o[e + 1])), f2), a, b);
+                o[e] = __float_as_uint(a);
+                o[e + 1] = __float_as_uint(b);
+              }
               tmem_st32(o_tmem + c * 32, o);
             }
           }
         }
         const float neg = (m_use == -INFINITY) ? 0.f : -m_use;
-        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+        const uint64_t sc2 = f2pack(sc, sc), neg2 = f2pack(neg, neg);
+        uint64_t sum_a = f2pack(0.f, 0.f), sum_b = f2pack(0.f, 0.f);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t pk[32];
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
             const int k = c * 64 + e * 2;
-            const float p0 = ex2(fmaf(__uint_as_float(s[k + 0]), sc, neg));
-            const float p1 = ex2(fmaf(__uint_as_float(s[k + 1]), sc, neg));
-            const float p2 = ex2(fmaf(__uint_as_float(s[k + 2]), sc, neg));
-            const float p3 = ex2(fmaf(__uint_as_float(s[k + 3]), sc, neg));
-            sum0 += p0;
-            sum1 += p1;
-            sum2 += p2;
-            sum3 += p3;
+            float x0, x1, x2, x3;
+            f2unpack(fma2(f2pack(__uint_as_float(s[k + 0]), __uint_as_float(s[k + 1])), sc2, neg2), x0, x1);
+            f2unpack(fma2(f2pack(__uint_as_float(s[k + 2]), __uint_as_float(s[k + 3])), sc2, neg2), x2, x3);
+            const float p0 = ex2(x0), p1 = ex2(x1), p2 = ex2(x2), p3 = ex2(x3);
+            sum_a = add2(sum_a, f2pack(p0, p1));
+            sum_b = add2(sum_b, f2pack(p2, p3));
             pk[e] = pack16<BF16>(p0, p1);
             pk[e + 1] = pack16<BF16>(p2, p3);
           }
@@ -352,7 +403,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&p_ready[i]);
-        l += (sum0 + sum1) + (sum2 + sum3);
+        {
+          float a, b;
+          f2unpack(add2(sum_a, sum_b), a, b);
+          l += a + b;
+        }
       }
 
       // ------------------------------ epilogue ------------------------------
