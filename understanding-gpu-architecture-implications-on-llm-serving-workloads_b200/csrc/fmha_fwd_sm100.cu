@@ -52,6 +52,7 @@ struct FmhaParams {
   int kv_len;      // valid keys (<= Skv); the K/V tensor maps end there
   int causal;
   int num_pairs;   // ceil(Sq / 256)
+  int head_major;  // CTA order: 0 = heaviest tile pairs of all heads first, 1 = all pairs of a head together
   float scale_log2;
   int* status;
 };
@@ -91,6 +92,32 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
+// 2^x for a pair of lanes on the FMA and integer pipes instead of the MUFU (which delivers only
+// 16 results per clock per SM: at one exponential per score it would be as busy as the tensor
+// pipe).  x = n + r with n = round(x), r in [-0.5, 0.5]; 2^r by a degree-3 minimax polynomial
+// (relative error 7.5e-5, below the half-ulp 4.9e-4 of the 16-bit P it is rounded to); 2^n is
+// added into the exponent field.  x is clamped at -125 so the exponent cannot wrap.
+__device__ __forceinline__ void ex2_emulated(uint64_t x2, float& p0, float& p1) {
+  float x0, x1;
+  f2unpack(x2, x0, x1);
+  x0 = fmaxf(x0, -125.f);
+  x1 = fmaxf(x1, -125.f);
+  x2 = f2pack(x0, x1);
+  const uint64_t magic = f2pack(12582912.f, 12582912.f);  // 1.5 * 2^23: forces rounding to an integer
+  const uint64_t j2 = add2(x2, magic);
+  const uint64_t n2 = add2(j2, f2pack(-12582912.f, -12582912.f));
+  const uint64_t r2 = fma2(n2, f2pack(-1.f, -1.f), x2);
+  uint64_t q2 = fma2(r2, f2pack(0.0551716648f, 0.0551716648f), f2pack(0.2426111251f, 0.2426111251f));
+  q2 = fma2(q2, r2, f2pack(0.6932609677f, 0.6932609677f));
+  q2 = fma2(q2, r2, f2pack(0.9999280572f, 0.9999280572f));
+  float q0, q1, j0, j1;
+  f2unpack(q2, q0, q1);
+  f2unpack(j2, j0, j1);
+  // the low mantissa bits of j hold n; (j << 23) drops the magic constant's own bits
+  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(j0) << 23));
+  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(j1) << 23));
+}
+
 template <int N>
 __device__ __forceinline__ void reg_alloc() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
@@ -138,11 +165,23 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int lane = threadIdx.x & 31;
 
   // ---- which work item ----
+  // CTA order.  When all K/V fit L2 comfortably the heaviest (latest, under the causal mask)
+  // tile pairs of every head go first, which balances the tail best.  Otherwise the tile
+  // pairs of one head run together (heavy first), so that the CTAs resident at one time
+  // share few K/V heads and those stay in L2 instead of being re-read from HBM per pair.
   const int idx = blockIdx.x;
-  const int h = idx % p.Hq;
-  const int t = idx / p.Hq;
-  const int b = t % p.B;
-  const int pair = p.num_pairs - 1 - t / p.B;  // heavy (late) causal tiles first
+  int h, b, pair;
+  if (p.head_major) {
+    pair = p.num_pairs - 1 - idx % p.num_pairs;
+    const int t = idx / p.num_pairs;
+    h = t % p.Hq;
+    b = t / p.Hq;
+  } else {
+    h = idx % p.Hq;
+    const int t = idx / p.Hq;
+    b = t % p.B;
+    pair = p.num_pairs - 1 - t / p.B;
+  }
   const int hk = h / (p.Hq / p.Hkv);
   const int off = p.kv_len - p.Sq;  // causal diagonal, aligned bottom-right
   int q0[2], nb[2];
@@ -389,10 +428,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
             const int k = c * 64 + e * 2;
-            float x0, x1, x2, x3;
+            // half of the exponentials on the MUFU, half on the FMA pipe
+            float x0, x1, p2, p3;
             f2unpack(fma2(f2pack(__uint_as_float(s[k + 0]), __uint_as_float(s[k + 1])), sc2, neg2), x0, x1);
-            f2unpack(fma2(f2pack(__uint_as_float(s[k + 2]), __uint_as_float(s[k + 3])), sc2, neg2), x2, x3);
-            const float p0 = ex2(x0), p1 = ex2(x1), p2 = ex2(x2), p3 = ex2(x3);
+            const float p0 = ex2(x0), p1 = ex2(x1);
+            ex2_emulated(fma2(f2pack(__uint_as_float(s[k + 2]), __uint_as_float(s[k + 3])), sc2, neg2), p2, p3);
             sum_a = add2(sum_a, f2pack(p0, p1));
             sum_b = add2(sum_b, f2pack(p2, p3));
             pk[e] = pack16<BF16>(p0, p1);
@@ -501,6 +541,9 @@ int launch_fmha(const void* Q, const void* K, const void* V, void* O, int B, int
   p.causal = causal;
   p.num_pairs = (Sq + 2 * kTile - 1) / (2 * kTile);
   p.scale_log2 = scale * 1.4426950408889634f;
+  // K and V of every (batch, kv head): 2 tensors x 2 bytes
+  const double kv_bytes = 4.0 * B * Hkv * (double)kv_len * D;
+  p.head_major = kv_bytes > 48.0 * 1024 * 1024 ? 1 : 0;
   p.status = status_ptr();
   if (!p.status) return B200K_ECUDA;
   const long grid = (long)p.num_pairs * Hq * B;
