@@ -39,7 +39,7 @@ def _rows_contiguous(t: torch.Tensor) -> torch.Tensor:
 
 
 def fmha_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = False, kv_len: int | None = None,
-             scale: float | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+             scale: float | None = None, out: torch.Tensor | None = None, variant: int = 0) -> torch.Tensor:
     """softmax(q k^T scale + mask) v; q [B,Hq,Sq,D], k, v [B,Hkv,Skv,D] (any batch/head/row strides)."""
     _check_qkv(q, k, v)
     B, Hq, Sq, D = q.shape
@@ -59,7 +59,7 @@ def fmha_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = F
     with torch.cuda.device(q.device):
         code = L.b200k_fmha_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, Hq, Hkv, Sq, Skv, D,
                                 _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(out),
-                                float(scale), int(bool(causal)), int(min(kv_len, Skv)), _DTYPES[q.dtype], 0,
+                                float(scale), int(bool(causal)), int(min(kv_len, Skv)), _DTYPES[q.dtype], int(variant),
                                 torch.cuda.current_stream(q.device).cuda_stream)
     _lib.check(code, "b200k_fmha_fwd")
     return out

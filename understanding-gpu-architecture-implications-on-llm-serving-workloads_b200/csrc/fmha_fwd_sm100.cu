@@ -16,7 +16,10 @@
 // row max, rescales O in TMEM only when the max grew by more than 2^8 (the
 // stale max is exact algebra: numerator and denominator carry the same factor),
 // writes P = exp2(s*scale*log2e - m) as 16-bit pairs over the S columns and adds
-// the row sum.  The epilogue scales O by 1/l, stages it in the (now free) Q tile
+// the row sum.  The MUFU delivers only 16 exponentials per clock per SM, which makes one
+// softmax pass about as long as the two MMAs of a tile; a quarter of the exponentials
+// therefore runs as a polynomial on the FMA pipe (measured +3 %; a half costs more issue
+// slots than it frees MUFU cycles).  The epilogue scales O by 1/l, stages it in the (now free) Q tile
 // and stores it with TMA, which also clips the ragged last tile.
 //
 // Reference semantics: kernels/fmha/pkg/fmha_unified/csrc/semi/fmha_2_nv.cu
@@ -35,6 +38,7 @@ namespace {
 constexpr int kFmhaThreads = 384;  // 2 softmax warpgroups + 1 warpgroup holding the TMA and MMA warps
 constexpr int kTile = 128;  // query rows per tile and keys per block
 constexpr float kRescaleThreshold = 8.0f;
+constexpr int kDefaultEmu = 1;  // of every 4 score pairs, how many exponentials run on the FMA pipe
 
 template <int D>
 struct FmhaSmem {
@@ -138,7 +142,8 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
   }
 }
 
-template <int D, bool BF16>
+// EMU: how many of every 4 score pairs take their exponentials on the FMA pipe (0, 1 or 2).
+template <int D, bool BF16, int EMU>
 __global__ void __launch_bounds__(kFmhaThreads, 1)
 fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
@@ -426,17 +431,27 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int c = 0; c < 2; ++c) {
           uint32_t pk[32];
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const int k = c * 64 + e * 2;
-            // half of the exponentials on the MUFU, half on the FMA pipe
-            float x0, x1, p2, p3;
-            f2unpack(fma2(f2pack(__uint_as_float(s[k + 0]), __uint_as_float(s[k + 1])), sc2, neg2), x0, x1);
-            const float p0 = ex2(x0), p1 = ex2(x1);
-            ex2_emulated(fma2(f2pack(__uint_as_float(s[k + 2]), __uint_as_float(s[k + 3])), sc2, neg2), p2, p3);
-            sum_a = add2(sum_a, f2pack(p0, p1));
-            sum_b = add2(sum_b, f2pack(p2, p3));
-            pk[e] = pack16<BF16>(p0, p1);
-            pk[e + 1] = pack16<BF16>(p2, p3);
+          for (int e = 0; e < 32; e += 4) {
+            // 8 scores = 4 pairs per step; the last EMU pairs go to the FMA pipe, the rest to the MUFU
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int k = c * 64 + (e + g) * 2;
+              const uint64_t x2 = fma2(f2pack(__uint_as_float(s[k]), __uint_as_float(s[k + 1])), sc2, neg2);
+              float p0, p1;
+              if (g >= 4 - EMU) {
+                ex2_emulated(x2, p0, p1);
+              } else {
+                float x0, x1;
+                f2unpack(x2, x0, x1);
+                p0 = ex2(x0);
+                p1 = ex2(x1);
+              }
+              if (g & 1)
+                sum_b = add2(sum_b, f2pack(p0, p1));
+              else
+                sum_a = add2(sum_a, f2pack(p0, p1));
+              pk[e + g] = pack16<BF16>(p0, p1);
+            }
           }
           tmem_st32(s_tmem + c * 32, pk);
         }
@@ -510,12 +525,12 @@ int make_map_bhsd(CUtensorMap* tm, const void* base, int D, int S, int H, int B,
   return encode_tmap_16bit(tm, base, 4, dims, strides, box, true);
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, int EMU>
 int launch_fmha(const void* Q, const void* K, const void* V, void* O, int B, int Hq, int Hkv, int Sq, int kv_len,
                 const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, float scale, int causal,
                 cudaStream_t stream) {
   using L = FmhaSmem<D>;
-  auto kfn = fmha_fwd_kernel<D, BF16>;
+  auto kfn = fmha_fwd_kernel<D, BF16, EMU>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -567,7 +582,6 @@ extern "C" int b200k_fmha_fwd(const void* Q, const void* K, const void* V, void*
                               int Skv, int D, const int64_t q_strides[3], const int64_t k_strides[3],
                               const int64_t v_strides[3], const int64_t o_strides[3], float scale, int causal,
                               int kv_len, int dtype, int variant, b200k_stream_t stream_) {
-  (void)variant;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (dtype != B200K_F16 && dtype != B200K_BF16) return B200K_EDTYPE;
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0 || Hq % Hkv != 0) return B200K_ESHAPE;
@@ -580,13 +594,17 @@ extern "C" int b200k_fmha_fwd(const void* Q, const void* K, const void* V, void*
     return B200K_EALIGN;
   if (!b200k_device_supported()) return B200K_ENOGPU;
   const bool bf16 = dtype == B200K_BF16;
-  if (D == 128)
-    return bf16 ? launch_fmha<128, true>(Q, K, V, O, B, Hq, Hkv, Sq, kv_len, q_strides, k_strides, v_strides,
-                                         o_strides, scale, causal, stream)
-                : launch_fmha<128, false>(Q, K, V, O, B, Hq, Hkv, Sq, kv_len, q_strides, k_strides, v_strides,
-                                          o_strides, scale, causal, stream);
-  return bf16 ? launch_fmha<64, true>(Q, K, V, O, B, Hq, Hkv, Sq, kv_len, q_strides, k_strides, v_strides, o_strides,
-                                      scale, causal, stream)
-              : launch_fmha<64, false>(Q, K, V, O, B, Hq, Hkv, Sq, kv_len, q_strides, k_strides, v_strides,
-                                       o_strides, scale, causal, stream);
+  // variant: 0 = default; 1, 2, 3 = 0, 1, 2 of every 4 score pairs take their exponential on the
+  // FMA pipe instead of the MUFU (kept selectable for ablation)
+  const int emu = variant == 0 ? kDefaultEmu : variant - 1;
+  if (emu < 0 || emu > 2) return B200K_EARG;
+#define B200K_FMHA(DD, BF, EM)                                                                                  \
+  launch_fmha<DD, BF, EM>(Q, K, V, O, B, Hq, Hkv, Sq, kv_len, q_strides, k_strides, v_strides, o_strides, scale, \
+                          causal, stream)
+#define B200K_FMHA_EMU(DD, BF) (emu == 0 ? B200K_FMHA(DD, BF, 0) : emu == 1 ? B200K_FMHA(DD, BF, 1) : B200K_FMHA(DD, BF, 2))
+  if (D == 128) return bf16 ? B200K_FMHA_EMU(128, true) : B200K_FMHA_EMU(128, false);
+  return bf16 ? B200K_FMHA_EMU(64, true) : B200K_FMHA_EMU(64, false);
+#undef B200K_FMHA_EMU
+#undef B200K_FMHA
 }
+
