@@ -185,6 +185,14 @@ int b200k_device_supported(void);
  * instruction descriptor: kind::f16, fp32 accumulate, major 0 = K, 1 = MN.
  * The reference has no counterpart (its kernels use WMMA fragments).
  */
+/*
+ * Failure-path self test: launches one warp that waits at most limit_ns (<= 100 ms)
+ * on a barrier nothing arrives on, records B200K_ETIMEOUT in the device status word
+ * (kernel id 15) and returns normally.  Nothing faults or hangs; after it,
+ * b200k_device_status() must report the expiry.  No counterpart in the reference.
+ */
+int b200k_debug_wait_timeout(uint64_t limit_ns, b200k_stream_t stream);
+
 uint64_t b200k_debug_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes);
 uint32_t b200k_debug_instr_desc(int dtype, int a_major, int b_major, int M, int N);
 

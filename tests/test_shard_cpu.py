@@ -82,3 +82,40 @@ def test_sharded_gemm_two_gloo_ranks(N):
             p.join(120)
             assert p.exitcode == 0
         assert dict(results) == {0: True, 1: True}
+
+
+def _preflight_worker(rank, world, port, mode, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    try:
+        desc = {"ok": True, "key": ("gemm", 8192, 4096, 11008)}
+        if mode == "shape_mismatch" and rank == 1:
+            desc["key"] = ("gemm", 8192, 4096, 4096)
+        if mode == "rank_failed" and rank == 1:
+            desc = {"ok": False, "error": "allocation failed", "key": None}
+        try:
+            shard.preflight_agree(desc)
+            results[rank] = "agreed"
+        except shard.ShardMismatch as e:
+            results[rank] = "mismatch"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode,expect", [("fine", "agreed"), ("shape_mismatch", "mismatch"), ("rank_failed", "mismatch")])
+def test_preflight_detects_host_injected_faults(mode, expect):
+    """Failures are injected on the host (a rank with a different shape, a rank that reports an
+    error) and must be detected on every rank before any launch or data-path collective."""
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        results = mgr.dict()
+        port = 31500 + (os.getpid() + len(mode)) % 2000
+        procs = [ctx.Process(target=_preflight_worker, args=(r, 2, port, mode, results)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(120)
+            assert p.exitcode == 0
+        assert dict(results) == {0: expect, 1: expect}

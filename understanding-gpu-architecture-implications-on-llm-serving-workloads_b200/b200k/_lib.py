@@ -39,6 +39,7 @@ SIGNATURES = {
     "b200k_device_status": (c_int, [POINTER(c_int), POINTER(c_int)]),
     "b200k_launch_count": (c_uint64, []),
     "b200k_device_supported": (c_int, []),
+    "b200k_debug_wait_timeout": (c_int, [c_uint64, c_void_p]),
     "b200k_debug_smem_desc": (c_uint64, [ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32]),
     "b200k_debug_instr_desc": (ctypes.c_uint32, [c_int, c_int, c_int, c_int, c_int]),
 }

@@ -89,6 +89,30 @@ def all_gather_columns(c_local: torch.Tensor, slabs: Sequence[Tuple[int, int]], 
     return out
 
 
+class ShardMismatch(RuntimeError):
+    """Ranks disagree about the problem they are about to run."""
+
+
+def preflight_agree(description, group=None, timeout_s: float = 30.0) -> None:
+    """Host-side agreement step run BEFORE any data-path launch or collective: every rank
+    publishes a small description of its shard (shapes, dtypes, slab bounds); all ranks
+    raise ShardMismatch if any rank reported something different from what rank 0 expects
+    of it, or reported a failure.  A rank that died or never arrives turns into the process
+    group's timeout error here, on the host, while no kernel or NCCL collective is in flight.
+    `description` is a dict with at least {"ok": bool, "key": hashable}; "key" must be equal
+    on all ranks."""
+    world = dist.get_world_size(group)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, description, group=group)
+    bad = [r for r, d in enumerate(gathered) if not d.get("ok", False)]
+    if bad:
+        raise ShardMismatch(f"ranks {bad} reported a failure before the launch: "
+                            f"{[gathered[r].get('error') for r in bad]}")
+    keys = {repr(d.get("key")) for d in gathered}
+    if len(keys) != 1:
+        raise ShardMismatch(f"ranks disagree about the problem: {sorted(keys)}")
+
+
 def sharded_gemm(a: torch.Tensor, b_full: torch.Tensor, gather: bool, matmul, group=None):
     """Rank-local slab of a @ b_full (and the gathered full product when `gather`).
     `matmul(a, b_slab)` is the local kernel (the library GEMM on GPU; torch.matmul in

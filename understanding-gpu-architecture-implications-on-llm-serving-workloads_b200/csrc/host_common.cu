@@ -103,9 +103,32 @@ const DevInfo& dev_info() {
   return infos[dev];
 }
 
+// One warp waits, with a caller-chosen limit, on an mbarrier that nothing ever arrives on, then
+// records the expiry in the status word and returns normally: exercises the path every bounded
+// wait of the real kernels takes when it gives up, without faulting or hanging anything.
+__global__ void wait_probe_kernel(uint64_t limit_ns, int* status) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && !mbar_wait_limit(&bar, 0, limit_ns)) report_timeout(status, KID_WAIT_PROBE, ROLE_PRODUCER);
+}
+
 }  // namespace b200k
 
 extern "C" {
+
+int b200k_debug_wait_timeout(uint64_t limit_ns, b200k_stream_t stream) {
+  if (!b200k_device_supported()) return B200K_ENOGPU;
+  if (limit_ns == 0 || limit_ns > 100000000ull) return B200K_EARG;  // at most 100 ms
+  int* status = b200k::status_ptr();
+  if (!status) return B200K_ECUDA;
+  b200k::wait_probe_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(limit_ns, status);
+  b200k::count_launch();
+  return b200k::check_launch();
+}
 
 const char* b200k_strerror(int code) {
   switch (code) {

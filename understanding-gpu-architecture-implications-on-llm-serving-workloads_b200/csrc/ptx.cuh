@@ -13,7 +13,7 @@ namespace b200k {
 // ---------------------------------------------------------------------------
 // device status word (one int[4] per device, owned by host_common.cu)
 // ---------------------------------------------------------------------------
-enum : int { KID_GEMM = 1, KID_GEMM2 = 2, KID_FMHA = 3, KID_DECODE = 4 };
+enum : int { KID_GEMM = 1, KID_GEMM2 = 2, KID_FMHA = 3, KID_DECODE = 4, KID_WAIT_PROBE = 15 };
 enum : int { ROLE_PRODUCER = 1, ROLE_MMA = 2, ROLE_EPILOGUE = 3, ROLE_SOFTMAX = 4, ROLE_CORRECTION = 5 };
 
 __device__ __forceinline__ void report_timeout(int* status, int kernel_id, int role) {
@@ -105,7 +105,7 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // far beyond any legitimate wait in these kernels.  The fast path (barrier
 // already complete) costs one try_wait.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
   if (mbar_test(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (;;) {
@@ -113,8 +113,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     for (int i = 0; i < 64; ++i) {
       if (mbar_test(bar, parity)) return true;
     }
-    if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+    if (global_timer_ns() - t0 > limit_ns) return false;
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  return mbar_wait_limit(bar, parity, kWaitLimitNs);
 }
 
 // ---------------------------------------------------------------------------
