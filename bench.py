@@ -50,7 +50,7 @@ UNIT = "TFLOP/s"
 FLOPS_PER_STEP = 2.0 * M * N * K
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the GEMM kernel on this
 # workload, from the ncu capture summarised in profiles/ (None until captured)
-NCU_TRAFFIC_BYTES = 647777536  # 480.5 MB read + 167.2 MB written (profiles/gemm_1cta_bf16_M8192_K4096_N11008.md)
+NCU_TRAFFIC_BYTES = 697283072  # 526.9 MB read + 170.4 MB written (ncu capture summarised under profiles/)
 
 
 def measured_peaks():
