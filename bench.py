@@ -385,6 +385,30 @@ def run_ours(args):
     except Exception as exc:  # the headline number stands even if an extra fails
         extra["error"] = repr(exc)[:300]
 
+    # ---- N > 1: the one collective of the GEMM path, reassembling a column-sharded product ----
+    if distributed:
+        try:
+            from b200k import shard
+            slabs = shard.gemm_column_slabs(N, world)
+            s0, e0 = slabs[rank]
+            w_slab = w[:, s0:e0]
+
+            def nccl_step():
+                shard.all_gather_columns(gemm.gemm(a, w_slab), slabs)
+
+            gsteps = max(5, min(steps, 20))
+            nccl_secs = max_over_ranks(time_cuda(nccl_step, gsteps, 3, barrier))
+            fused = shard.FusedAllGatherGemm(M, N, torch.bfloat16, dev)
+            fused_secs = max_over_ranks(time_cuda(lambda: fused(a, w_slab), gsteps, 3, barrier))
+            extra["gemm_allgather_strong"] = {
+                "workload": f"C[{M},{N}] = A . W with W column-sharded over {world} GPUs, full C on every rank",
+                "nccl_ms": nccl_secs / gsteps * 1e3, "fused_epilogue_ms": fused_secs / gsteps * 1e3,
+                "tflops_fused": FLOPS_PER_STEP * gsteps / fused_secs / 1e12,
+                "note": "nccl = local slab GEMM + all_gather_into_tensor + column reassembly; fused = epilogue TMA "
+                        "stores into all ranks' symmetric buffers + symmetric-memory barrier"}
+        except Exception as exc:
+            extra["gemm_allgather_strong"] = {"error": repr(exc)[:300]}
+
     # ---- CPU baseline on rank 0 at N=1 ----
     cpu = None
     if world == 1 and rank == 0 and not args.no_cpu_baseline:

@@ -72,6 +72,23 @@ int b200k_gemm(const void* A_device, const void* B_device, void* C_device,
                void* workspace_device, size_t workspace_bytes,
                b200k_stream_t stream);
 
+/*
+ * The same product, stored to num_dst (1..8) destinations: C_dsts[i] points at the
+ * first element of the [M,N] window inside destination i (all with leading dimension
+ * ldc).  With the destinations being the full-width C buffers of the GPUs of one
+ * node, mapped into this process (CUDA peer / symmetric memory), rank r computes
+ * its column slab of a sharded weight and the epilogue writes every finished tile
+ * into all ranks' buffers over NVLink with TMA stores while later tiles are still
+ * being computed: GEMM and all-gather in one kernel.  The caller synchronises the
+ * ranks afterwards (a barrier) before anyone reads C.  Tensor-core variants only
+ * (16-byte alignment rules of b200k_gemm apply to every destination).
+ * No counterpart in the reference, which has no multi-GPU path.
+ */
+int b200k_gemm_scatter(const void* A_device, const void* B_device, void* const* C_dsts,
+                       int num_dst, int M, int N, int K,
+                       int64_t lda, int64_t ldb, int64_t ldc, int dtype,
+                       b200k_stream_t stream);
+
 /* Bytes of workspace b200k_gemm needs for (M,N,K,variant); 0 when none. */
 size_t b200k_gemm_workspace_bytes(int M, int N, int K, int variant);
 

@@ -125,3 +125,44 @@ def sharded_gemm(a: torch.Tensor, b_full: torch.Tensor, gather: bool, matmul, gr
     if not gather:
         return c_local, slabs
     return all_gather_columns(c_local, slabs, group), slabs
+
+
+class FusedAllGatherGemm:
+    """C = a @ b_full reassembled on every rank by the GEMM epilogue itself: rank r computes
+    its column slab and stores every finished tile into the C buffers of all ranks, which live
+    in symmetric (peer-mapped) memory; a symmetric-memory barrier then orders the ranks.  No NCCL
+    collective and no multicast load is involved: the data crosses NVLink as plain TMA stores
+    while later tiles are still being computed.  GPU only (needs the library)."""
+
+    def __init__(self, M: int, N: int, dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > 8:
+            raise RuntimeError("at most 8 destinations (one node)")
+        self.M, self.N = M, N
+        self.slabs = gemm_column_slabs(N, self.world)
+        self.c_full = symm_mem.empty((M, N), dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.c_full, self.group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+
+    def __call__(self, a: torch.Tensor, b_slab: torch.Tensor) -> torch.Tensor:
+        """a [M,K]; b_slab = this rank's columns of the weight, [K, slab width].  Returns the
+        full C [M,N] (this rank's symmetric buffer), valid on return in stream order."""
+        import ctypes
+        from . import _lib
+        from .gemm import _DTYPES
+        s, e = self.slabs[self.rank]
+        if b_slab.size(1) != e - s or a.size(0) != self.M or a.size(1) != b_slab.size(0):
+            raise RuntimeError("operand shapes do not match this rank's slab")
+        if e > s:
+            esz = self.c_full.element_size()
+            dsts = (ctypes.c_void_p * self.world)(*[p + s * esz for p in self.ptrs])
+            code = _lib.lib().b200k_gemm_scatter(
+                a.data_ptr(), b_slab.data_ptr(), dsts, self.world, self.M, e - s, a.size(1),
+                a.stride(0), b_slab.stride(0), self.N, _DTYPES[a.dtype],
+                torch.cuda.current_stream(a.device).cuda_stream)
+            _lib.check(code, "b200k_gemm_scatter")
+        self.handle.barrier()
+        return self.c_full

@@ -69,10 +69,18 @@ struct GemmSmem {
   static constexpr uint32_t kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
 };
 
+// Output tensor maps: normally one.  With several, every finished tile is stored to each of them
+// (the same [M,N] window in the C buffers of several GPUs, reached through peer-mapped memory),
+// which reassembles a column-sharded product on all ranks from inside the epilogue.
+constexpr int kMaxDst = 8;
+struct GemmOutMaps {
+  CUtensorMap m[kMaxDst];
+};
+
 template <int CTAS, int BN, int STAGES, bool BF16>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int* status) {
+               const __grid_constant__ GemmOutMaps tmC, int num_dst, int M, int N, int K, int* status) {
   using L = GemmSmem<CTAS, BN, STAGES>;
   constexpr uint32_t kTmemCols = 2 * BN;
   constexpr int kTileM = kBM * CTAS;
@@ -108,7 +116,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     fence_mbar_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
-    prefetch_tmap(&tmC);
+    for (int d = 0; d < num_dst; ++d) prefetch_tmap(&tmC.m[d]);
   }
   if (warp == 1) {
     tmem_alloc<CTAS>(tmem_holder, kTmemCols);
@@ -260,7 +268,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         __syncwarp();
         const int col0 = nb * BN + c * 64;
         if (lane == 0 && row0 < M && col0 < N) {
-          tma_store_2d(&tmC, buf, col0, row0);
+          for (int d = 0; d < num_dst; ++d) tma_store_2d(&tmC.m[d], buf, col0, row0);
           tma_store_commit();
         }
       }
@@ -350,8 +358,8 @@ gemm_generic_kernel(const void* __restrict__ A, const void* __restrict__ B, void
 }
 
 template <int CTAS, int BN, int STAGES, bool BF16>
-int launch_tc(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
-              cudaStream_t stream) {
+int launch_tc(const void* A, const void* B, void* const* Cs, int num_dst, int M, int N, int K, int64_t lda,
+              int64_t ldb, int64_t ldc, cudaStream_t stream) {
   using L = GemmSmem<CTAS, BN, STAGES>;
   auto kfn = gemm_tc_kernel<CTAS, BN, STAGES, BF16>;
   static bool configured[64] = {};
@@ -364,7 +372,8 @@ int launch_tc(const void* A, const void* B, void* C, int M, int N, int K, int64_
     }
     configured[dev & 63] = true;
   }
-  CUtensorMap tmA, tmB, tmC;
+  CUtensorMap tmA, tmB;
+  GemmOutMaps tmC;
   {
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
     uint64_t str[1] = {(uint64_t)lda * 2};
@@ -379,11 +388,12 @@ int launch_tc(const void* A, const void* B, void* C, int M, int N, int K, int64_
     int r = encode_tmap_16bit(&tmB, B, 2, dims, str, box, true);
     if (r) return r;
   }
-  {
+  for (int d = 0; d < kMaxDst; ++d) {
+    // unused slots repeat the first map so that the parameter block holds no garbage
     uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
     uint64_t str[1] = {(uint64_t)ldc * 2};
     uint32_t box[2] = {64, 32};
-    int r = encode_tmap_16bit(&tmC, C, 2, dims, str, box, true);
+    int r = encode_tmap_16bit(&tmC.m[d], Cs[d < num_dst ? d : 0], 2, dims, str, box, true);
     if (r) return r;
   }
   int* status = status_ptr();
@@ -403,7 +413,7 @@ int launch_tc(const void* A, const void* B, void* C, int M, int N, int K, int64_
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kfn, tmA, tmB, tmC, M, N, K, status);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kfn, tmA, tmB, tmC, num_dst, M, N, K, status);
   count_launch();
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
@@ -470,20 +480,40 @@ extern "C" int b200k_gemm(const void* A, const void* B, void* C, int M, int N, i
       return launch_skinny(A, B, C, M, N, K, lda, ldb, ldc, bf16, stream);
     case B200K_GEMM_1CTA:
       if (!tma_ok) return B200K_EALIGN;
-      return bf16 ? launch_tc<1, 256, 4, true>(A, B, C, M, N, K, lda, ldb, ldc, stream)
-                  : launch_tc<1, 256, 4, false>(A, B, C, M, N, K, lda, ldb, ldc, stream);
+      return bf16 ? launch_tc<1, 256, 4, true>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream)
+                  : launch_tc<1, 256, 4, false>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream);
     case B200K_GEMM_2CTA:
       if (!tma_ok) return B200K_EALIGN;
-      return bf16 ? launch_tc<2, 256, 6, true>(A, B, C, M, N, K, lda, ldb, ldc, stream)
-                  : launch_tc<2, 256, 6, false>(A, B, C, M, N, K, lda, ldb, ldc, stream);
+      return bf16 ? launch_tc<2, 256, 6, true>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream)
+                  : launch_tc<2, 256, 6, false>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream);
     case B200K_GEMM_1CTA_N128:
       if (!tma_ok) return B200K_EALIGN;
-      return bf16 ? launch_tc<1, 128, 6, true>(A, B, C, M, N, K, lda, ldb, ldc, stream)
-                  : launch_tc<1, 128, 6, false>(A, B, C, M, N, K, lda, ldb, ldc, stream);
+      return bf16 ? launch_tc<1, 128, 6, true>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream)
+                  : launch_tc<1, 128, 6, false>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream);
     case B200K_GEMM_GENERIC:
       return bf16 ? launch_generic<true>(A, B, C, M, N, K, lda, ldb, ldc, stream)
                   : launch_generic<false>(A, B, C, M, N, K, lda, ldb, ldc, stream);
     default:
       return B200K_EARG;
   }
+}
+
+extern "C" int b200k_gemm_scatter(const void* A, const void* B, void* const* C_dsts, int num_dst, int M, int N, int K,
+                                  int64_t lda, int64_t ldb, int64_t ldc, int dtype, b200k_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (dtype != B200K_F16 && dtype != B200K_BF16) return B200K_EDTYPE;
+  if (M <= 0 || N <= 0 || K <= 0 || lda < K || ldb < N || ldc < N) return B200K_ESHAPE;
+  if (!A || !B || !C_dsts || num_dst < 1 || num_dst > kMaxDst) return B200K_EARG;
+  if (!aligned16(A) || !aligned16(B) || lda % 8 || ldb % 8 || ldc % 8) return B200K_EALIGN;
+  for (int d = 0; d < num_dst; ++d)
+    if (!C_dsts[d] || !aligned16(C_dsts[d])) return B200K_EALIGN;
+  if (!b200k_device_supported()) return B200K_ENOGPU;
+  const int sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
+  const long pair_tiles = (long)((M + 255) / 256) * ((N + 255) / 256);
+  const bool bf16 = dtype == B200K_BF16;
+  if (pair_tiles >= sms / 2)
+    return bf16 ? launch_tc<2, 256, 6, true>(A, B, C_dsts, num_dst, M, N, K, lda, ldb, ldc, stream)
+                : launch_tc<2, 256, 6, false>(A, B, C_dsts, num_dst, M, N, K, lda, ldb, ldc, stream);
+  return bf16 ? launch_tc<1, 128, 6, true>(A, B, C_dsts, num_dst, M, N, K, lda, ldb, ldc, stream)
+              : launch_tc<1, 128, 6, false>(A, B, C_dsts, num_dst, M, N, K, lda, ldb, ldc, stream);
 }
