@@ -43,12 +43,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, vari
     if K == 0:
         return out.zero_()
     L = _lib.lib()
-    with torch.cuda.device(a.device):
-        ws_bytes = L.b200k_gemm_workspace_bytes(M, N, K, variant)
-        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device) if ws_bytes else None
-        code = L.b200k_gemm(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K,
-                            a.stride(0), b.stride(0), out.stride(0), _DTYPES[a.dtype], variant,
-                            ws.data_ptr() if ws is not None else None, ws_bytes,
-                            torch.cuda.current_stream(a.device).cuda_stream)
-    _lib.check(code, "b200k_gemm")
+    dev_index = a.device.index
+    if dev_index is not None and dev_index != torch.cuda.current_device():
+        with torch.cuda.device(a.device):
+            return gemm(a, b, out=out, variant=variant)
+    # no variant needs a workspace (split-K partials stay in shared memory), so none is allocated
+    code = L.b200k_gemm(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K,
+                        a.stride(0), b.stride(0), out.stride(0), _DTYPES[a.dtype], variant,
+                        None, 0, torch.cuda.current_stream().cuda_stream)
+    if code:
+        _lib.check(code, "b200k_gemm")
     return out

@@ -1,0 +1,121 @@
+"""Performance sweep over the five benchmark configurations, one JSON line per case.
+
+    python -m b200k.sweep [--quick] [--out results.jsonl]
+
+The counterpart of the reference's perf sweeps (kernels/gemm/test/perf.py:62-77,
+kernels/fmha/test/perf.py:100-113), which print a TFLOPS table per kernel index; here every
+case is timed with CUDA events (3 warm-ups, >= 10 launches; weights of memory-bound GEMMs are
+rotated through 8 copies so they stream from HBM), next to the library comparators the
+reference also uses as its kernels -1 / -2 (torch.matmul, scaled_dot_product_attention).
+Rates: TFLOP/s = 2MNK/t (GEMM), 4*B*H*Sq*Skv*D/t, halved when causal (FMHA; the reference's
+script does not halve); GB/s = algorithmic bytes / t.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+import torch.nn.functional as F
+
+from . import fmha, gemm, inputs
+
+
+def _time(fn, n):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / n / 1e3
+
+
+def gemm_case(M, K, N, dtype, dev, n=20):
+    copies = 8 if M <= 128 else 1
+    a = inputs.device_randn16((M, K), 1, 1.0, dtype, dev)
+    ws = [inputs.device_randn16((K, N), 2 + i, 0.02, dtype, dev) for i in range(copies)]
+    out = torch.empty((M, N), dtype=dtype, device=dev)
+    turn = [0]
+
+    def ours():
+        turn[0] = (turn[0] + 1) % copies
+        gemm.gemm(a, ws[turn[0]], out=out)
+
+    def lib():
+        turn[0] = (turn[0] + 1) % copies
+        torch.matmul(a, ws[turn[0]], out=out)
+
+    n = n if M > 128 else 4 * n
+    t, t_lib = _time(ours, n), _time(lib, n)
+    flops, nbytes = 2.0 * M * N * K, 2.0 * (M * K + K * N + M * N)
+    return {"path": "gemm", "M": M, "K": K, "N": N, "dtype": str(dtype).split(".")[-1], "us": t * 1e6,
+            "tflops": flops / t / 1e12, "gbs": nbytes / t / 1e9, "cublas_tflops": flops / t_lib / 1e12,
+            "cublas_gbs": nbytes / t_lib / 1e9}
+
+
+def fmha_case(B, Hq, Hkv, S, D, causal, dtype, dev, n=10):
+    q = inputs.device_randn16((B, Hq, S, D), 1, 1.0, dtype, dev)
+    k = inputs.device_randn16((B, Hkv, S, D), 2, 1.0, dtype, dev)
+    v = inputs.device_randn16((B, Hkv, S, D), 3, 1.0, dtype, dev)
+    out = torch.empty_like(q)
+    t = _time(lambda: fmha.fmha_fwd(q, k, v, causal=causal, out=out), n)
+    t_lib = _time(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=causal, enable_gqa=True), n)
+    flops = 4.0 * B * Hq * S * S * D * (0.5 if causal else 1.0)
+    return {"path": "fmha", "B": B, "Hq": Hq, "Hkv": Hkv, "S": S, "D": D, "causal": causal,
+            "dtype": str(dtype).split(".")[-1], "us": t * 1e6, "tflops": flops / t / 1e12,
+            "sdpa_tflops": flops / t_lib / 1e12}
+
+
+def decode_case(dev, B=64, n=10):
+    Hq, Hkv, Skv, D = 32, 8, 32768, 128
+    lens = inputs.decode_lens(64)[:B].to(dev)
+    q = inputs.device_randn16((B, Hq, 1, D), 7, 1.0, torch.float16, dev)
+    k = inputs.device_randn16((B, Hkv, Skv, D), 8, 1.0, torch.float16, dev)
+    v = inputs.device_randn16((B, Hkv, Skv, D), 9, 1.0, torch.float16, dev)
+    out = torch.empty_like(q)
+    ws = fmha.decode_workspace(B, Hq, Hkv, 1, Skv, D, 0, dev)
+    t = _time(lambda: fmha.fmha_decode(q, k, v, kv_lens=lens, out=out, workspace=ws), n)
+    nbytes = float(lens.sum().item()) * Hkv * D * 4 + 2.0 * B * Hq * D * 2
+    return {"path": "decode", "B": B, "Hq": Hq, "Hkv": Hkv, "Skv": Skv, "D": D, "sum_len": int(lens.sum().item()),
+            "us": t * 1e6, "gbs": nbytes / t / 1e9}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--quick", action="store_true", help="one dtype, fewer shapes")
+    ap.add_argument("--out", default=None)
+    args = ap.parse_args(argv)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    sink = open(args.out, "w") if args.out else None
+
+    def emit(rec):
+        line = json.dumps(rec)
+        print(line, flush=True)
+        if sink:
+            sink.write(line + "\n")
+            sink.flush()
+
+    emit(gemm_case(1024, 1024, 1024, torch.float16, dev, n=50))
+    dtypes = [torch.bfloat16] if args.quick else [torch.bfloat16, torch.float16]
+    for dtype in dtypes:
+        for (K, N) in inputs.LLAMA7B_KN:
+            for M in inputs.LLM_M + [64]:
+                emit(gemm_case(M, K, N, dtype, dev))
+    emit(fmha_case(1, 32, 8, 4096, 128, True, torch.float16, dev, n=30))
+    for D in (64, 128):
+        for S in ((2048,) if args.quick else (1024, 2048, 8192)):
+            for causal in (False, True):
+                emit(fmha_case(8, 32, 32, S, D, causal, torch.bfloat16, dev))
+    emit(decode_case(dev))
+    if sink:
+        sink.close()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -34,10 +34,61 @@ EncodeTiledFn encode_fn() {
 }
 }  // namespace
 
+namespace {
+// Small cache of encoded tensor maps: serving loops call with the same operands over and over,
+// and an encode costs about as much as the rest of a launch.  Keyed by everything that enters
+// the encoding; a map is a pure function of the key, so a stale entry cannot be wrong.
+struct TmapKey {
+  const void* base;
+  int rank;
+  bool swizzle;
+  uint64_t dims[4];
+  uint64_t strides[3];
+  uint32_t box[4];
+  bool operator==(const TmapKey& o) const {
+    if (base != o.base || rank != o.rank || swizzle != o.swizzle) return false;
+    for (int i = 0; i < rank; ++i)
+      if (dims[i] != o.dims[i] || box[i] != o.box[i] || (i + 1 < rank && strides[i] != o.strides[i])) return false;
+    return true;
+  }
+};
+constexpr int kTmapCacheSize = 64;
+struct TmapCache {
+  TmapKey keys[kTmapCacheSize];
+  CUtensorMap maps[kTmapCacheSize];
+  bool used[kTmapCacheSize] = {};
+  unsigned next = 0;
+  std::mutex mu;
+};
+TmapCache& tmap_cache() {
+  static TmapCache c;
+  return c;
+}
+}  // namespace
+
 int encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                       const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return B200K_ECUDA;
+  if (rank < 1 || rank > 4) return B200K_ETMAP;
+  TmapKey key{};
+  key.base = base;
+  key.rank = rank;
+  key.swizzle = swizzle128;
+  for (int i = 0; i < rank; ++i) {
+    key.dims[i] = dims[i];
+    key.box[i] = box[i];
+    if (i + 1 < rank) key.strides[i] = strides_bytes[i];
+  }
+  TmapCache& cache = tmap_cache();
+  {
+    std::lock_guard<std::mutex> lock(cache.mu);
+    for (int i = 0; i < kTmapCacheSize; ++i)
+      if (cache.used[i] && cache.keys[i] == key) {
+        *out = cache.maps[i];
+        return B200K_OK;
+      }
+  }
   cuuint64_t gdims[5];
   cuuint64_t gstrides[4];
   cuuint32_t gbox[5];
@@ -54,7 +105,15 @@ int encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64
                   gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? B200K_OK : B200K_ETMAP;
+  if (r != CUDA_SUCCESS) return B200K_ETMAP;
+  {
+    std::lock_guard<std::mutex> lock(cache.mu);
+    const unsigned slot = cache.next++ % kTmapCacheSize;
+    cache.keys[slot] = key;
+    cache.maps[slot] = *out;
+    cache.used[slot] = true;
+  }
+  return B200K_OK;
 }
 
 int* status_ptr() {
