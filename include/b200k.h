@@ -89,6 +89,22 @@ int b200k_gemm_scatter(const void* A_device, const void* B_device, void* const* 
                        int64_t lda, int64_t ldb, int64_t ldc, int dtype,
                        b200k_stream_t stream);
 
+/*
+ * GEMM with an epilogue fused into the accumulator drain (tensor-core variants only,
+ * alignment rules of b200k_gemm):
+ *   B200K_EPI_ADD     C[M,N]   = A.B + R            R: [M,N], leading dimension ldr (residual add)
+ *   B200K_EPI_SWIGLU  C[M,N/2] = silu(P[:,2j]) * P[:,2j+1], P = A.B: B holds the gate and up
+ *                     projections with interleaved columns (gate_j at 2j, up_j at 2j+1); N % 16 == 0
+ * These are the fusions a Llama layer needs around its projections (residual after o_proj and
+ * down_proj, SiLU(gate)*up after the merged gate/up projection); the reference applies its
+ * GEMMs to no model and fuses nothing (its only fusion is attention itself), so they have no
+ * counterpart there.
+ */
+enum { B200K_EPI_ADD = 1, B200K_EPI_SWIGLU = 2 };
+int b200k_gemm_fused(const void* A_device, const void* B_device, void* C_device, const void* R_device,
+                     int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr,
+                     int dtype, int epilogue, b200k_stream_t stream);
+
 /* Bytes of workspace b200k_gemm needs for (M,N,K,variant); 0 when none. */
 size_t b200k_gemm_workspace_bytes(int M, int N, int K, int variant);
 

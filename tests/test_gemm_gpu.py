@@ -172,3 +172,48 @@ def test_error_codes(cuda_device):
     with pytest.raises(RuntimeError):  # tensor-core variant on a misaligned leading dimension
         gemm.gemm(torch.zeros(8, 9, dtype=torch.float16, device=cuda_device)[:, :8],
                   torch.zeros(8, 9, dtype=torch.float16, device=cuda_device)[:, :8], variant=1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (300, 520, 200), (1024, 4096, 512), (4096, 4096, 1024)])
+def test_fused_residual_add(cuda_device, shape, dtype):
+    """C = A.B + R with the add in the epilogue (fp32 before the single rounding): small shapes take
+    the 128x128 kernel, the last one the CTA-pair kernel; ragged edges included."""
+    from b200k import gemm
+    M, N, K = shape
+    a, b = _inputs(M, N, K, dtype, seed=M + N + K, std_b=0.1)
+    g = torch.Generator().manual_seed(77)
+    r = torch.randn(M, N, generator=g).to(dtype)
+    c = gemm.gemm_add(a.to(cuda_device), b.to(cuda_device), r.to(cuda_device))
+    ref = oracle.gemm_ref(a, b) + r.float()
+    assert oracle.rel_frobenius(c, ref) <= TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (300, 264, 200), (512, 2048, 512), (4096, 2048, 1024)])
+def test_fused_swiglu(cuda_device, shape, dtype):
+    """C = silu(A.Wg) * (A.Wu) from one GEMM over the column-interleaved [Wg|Wu] weight."""
+    from b200k import gemm
+    M, F, K = shape
+    g = torch.Generator().manual_seed(M + F + K)
+    a = torch.randn(M, K, generator=g).to(dtype)
+    wg = (torch.randn(K, F, generator=g) * 0.1).to(dtype)
+    wu = (torch.randn(K, F, generator=g) * 0.1).to(dtype)
+    w = gemm.interleave_gate_up(wg, wu)
+    assert torch.equal(w[:, 0::2], wg) and torch.equal(w[:, 1::2], wu)
+    c = gemm.gemm_swiglu(a.to(cuda_device), w.to(cuda_device))
+    assert c.shape == (M, F)
+    gate, up = oracle.gemm_ref(a, wg), oracle.gemm_ref(a, wu)
+    ref = torch.nn.functional.silu(gate) * up
+    assert oracle.rel_frobenius(c, ref) <= TOL
+
+
+def test_fused_argument_errors(cuda_device):
+    from b200k import _lib, gemm
+    a = torch.zeros(128, 64, dtype=torch.float16, device=cuda_device)
+    b = torch.zeros(64, 72, dtype=torch.float16, device=cuda_device)
+    with pytest.raises(_lib.B200KError) as e:          # N = 72 is not a multiple of 16
+        gemm.gemm_swiglu(a, b)
+    assert e.value.code == -2
+    with pytest.raises(RuntimeError):
+        gemm.gemm_add(a, b, torch.zeros(128, 64, dtype=torch.float16, device=cuda_device))

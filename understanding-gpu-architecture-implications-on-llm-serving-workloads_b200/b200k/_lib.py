@@ -25,6 +25,8 @@ SIGNATURES = {
                            c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "b200k_gemm_scatter": (c_int, [c_void_p, c_void_p, POINTER(c_void_p), c_int, c_int, c_int, c_int, c_int64,
                                    c_int64, c_int64, c_int, c_void_p]),
+    "b200k_gemm_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64,
+                                 c_int64, c_int64, c_int, c_int, c_void_p]),
     "b200k_gemm_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "b200k_fmha_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                _I64x3, _I64x3, _I64x3, _I64x3, c_float, c_int, c_int, c_int, c_int, c_void_p]),

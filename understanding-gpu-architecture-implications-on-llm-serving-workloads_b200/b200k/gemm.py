@@ -54,3 +54,52 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, vari
     if code:
         _lib.check(code, "b200k_gemm")
     return out
+
+
+EPI_ADD, EPI_SWIGLU = 1, 2
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """[K,F] gate and up projection weights -> one [K,2F] weight with gate_j at column 2j and up_j
+    at column 2j+1 (a one-time weight transform), the layout the SwiGLU epilogue expects."""
+    K, F = w_gate.shape
+    return torch.stack((w_gate, w_up), dim=2).reshape(K, 2 * F).contiguous()
+
+
+def _fused(a, b, residual, epilogue, out):
+    _check_inputs(a, b)
+    if a.stride(1) != 1:
+        a = a.contiguous()
+    if b.stride(1) != 1:
+        b = b.contiguous()
+    M, K = a.shape
+    N = b.size(1)
+    n_out = N // 2 if epilogue == EPI_SWIGLU else N
+    if out is None:
+        out = torch.empty((M, n_out), dtype=a.dtype, device=a.device)
+    elif out.shape != (M, n_out) or out.dtype != a.dtype or out.stride(1) != 1:
+        raise RuntimeError("out has the wrong shape, dtype or layout")
+    if residual is not None:
+        if residual.shape != (M, N) or residual.dtype != a.dtype or residual.device != a.device:
+            raise RuntimeError("residual must be [M,N] with the operands' dtype and device")
+        if residual.stride(1) != 1:
+            residual = residual.contiguous()
+    if M == 0 or N == 0:
+        return out
+    with torch.cuda.device(a.device):
+        code = _lib.lib().b200k_gemm_fused(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), residual.data_ptr() if residual is not None else None,
+            M, N, K, a.stride(0), b.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
+            _DTYPES[a.dtype], epilogue, torch.cuda.current_stream(a.device).cuda_stream)
+    _lib.check(code, "b200k_gemm_fused")
+    return out
+
+
+def gemm_add(a: torch.Tensor, b: torch.Tensor, residual: torch.Tensor, out: torch.Tensor | None = None):
+    """a @ b + residual with the add fused into the GEMM epilogue (fp32 before rounding)."""
+    return _fused(a, b, residual, EPI_ADD, out)
+
+
+def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor | None = None):
+    """silu(a @ w_gate) * (a @ w_up) for w_gate_up = interleave_gate_up(w_gate, w_up), fused."""
+    return _fused(a, w_gate_up, None, EPI_SWIGLU, out)

@@ -424,8 +424,8 @@ int launch_decode(const void* Q, const void* K, const void* V, void* O, int B, i
     uint64_t kstr[3] = {(uint64_t)ks[2] * 2, (uint64_t)ks[1] * 2, (uint64_t)ks[0] * 2};
     uint64_t vstr[3] = {(uint64_t)vs[2] * 2, (uint64_t)vs[1] * 2, (uint64_t)vs[0] * 2};
     int r;
-    if ((r = encode_tmap_16bit(&tmK, K, 4, dims, kstr, box, true))) return r;
-    if ((r = encode_tmap_16bit(&tmV, V, 4, dims, vstr, box, true))) return r;
+    if ((r = encode_tmap_16bit(&tmK, K, 4, dims, kstr, box, 1))) return r;
+    if ((r = encode_tmap_16bit(&tmV, V, 4, dims, vstr, box, 1))) return r;
   }
   DecParams p;
   p.q = Q;

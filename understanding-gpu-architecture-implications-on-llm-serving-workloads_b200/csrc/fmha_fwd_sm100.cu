@@ -522,7 +522,7 @@ int make_map_bhsd(CUtensorMap* tm, const void* base, int D, int S, int H, int B,
   uint64_t dims[4] = {(uint64_t)D, (uint64_t)S, (uint64_t)H, (uint64_t)B};
   uint64_t strides[3] = {(uint64_t)st[2] * 2, (uint64_t)st[1] * 2, (uint64_t)st[0] * 2};
   uint32_t box[4] = {64, (uint32_t)kTile, 1, 1};
-  return encode_tmap_16bit(tm, base, 4, dims, strides, box, true);
+  return encode_tmap_16bit(tm, base, 4, dims, strides, box, 1);
 }
 
 template <int D, bool BF16, int EMU>

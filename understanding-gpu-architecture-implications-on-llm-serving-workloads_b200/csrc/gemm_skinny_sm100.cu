@@ -290,14 +290,14 @@ static int launch_skinny_t(const void* A, const void* B, void* C, int M, int N, 
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
     uint64_t str[1] = {(uint64_t)lda * 2};
     uint32_t box[2] = {kSkBK, (uint32_t)MPAD};
-    int r = encode_tmap_16bit(&tmX, A, 2, dims, str, box, true);
+    int r = encode_tmap_16bit(&tmX, A, 2, dims, str, box, 1);
     if (r) return r;
   }
   {
     uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
     uint64_t str[1] = {(uint64_t)ldb * 2};
     uint32_t box[2] = {64, kSkBK};
-    int r = encode_tmap_16bit(&tmW, B, 2, dims, str, box, true);
+    int r = encode_tmap_16bit(&tmW, B, 2, dims, str, box, 1);
     if (r) return r;
   }
   int* status = status_ptr();

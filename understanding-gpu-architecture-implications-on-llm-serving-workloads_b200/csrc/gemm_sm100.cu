@@ -77,10 +77,33 @@ struct GemmOutMaps {
   CUtensorMap m[kMaxDst];
 };
 
-template <int CTAS, int BN, int STAGES, bool BF16>
+// Epilogues fused into the accumulator drain:
+//   kEpiNone    C = A.B
+//   kEpiAdd     C = A.B + R               (residual add; R is [M,N] with leading dimension ldr)
+//   kEpiSwiglu  C[:, j] = silu(P[:, 2j]) * P[:, 2j+1] with P = A.B: the weight holds the gate and up
+//               projections with their columns interleaved, C has N/2 columns
+constexpr int kEpiNone = 0, kEpiAdd = 1, kEpiSwiglu = 2;
+
+template <bool BF16>
+__device__ __forceinline__ void unpack2(uint32_t u, float& lo, float& hi) {
+  if constexpr (BF16) {
+    lo = __uint_as_float(u << 16);
+    hi = __uint_as_float(u & 0xffff0000u);
+  } else {
+    const __half2 h = *reinterpret_cast<const __half2*>(&u);
+    lo = __low2float(h);
+    hi = __high2float(h);
+  }
+}
+__device__ __forceinline__ float silu_mul(float gate, float up) {
+  return __fdividef(gate, 1.f + __expf(-gate)) * up;
+}
+
+template <int CTAS, int BN, int STAGES, bool BF16, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ GemmOutMaps tmC, int num_dst, int M, int N, int K, int* status) {
+               const __grid_constant__ GemmOutMaps tmC, int num_dst, int M, int N, int K, int* status,
+               const uint16_t* __restrict__ R, int64_t ldr) {
   using L = GemmSmem<CTAS, BN, STAGES>;
   constexpr uint32_t kTmemCols = 2 * BN;
   constexpr int kTileM = kBM * CTAS;
@@ -243,33 +266,85 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tmem_ld32(taddr + 32, w);
         tmem_ld_wait();
         uint8_t* buf = stg + (c & 1) * 4096;
+        const int col0 = nb * BN + c * 64;
+        if constexpr (EPI == kEpiAdd) {
+          // this thread's row of the residual, 64 columns = 8 chunks of 8 elements
+          const int grow = row0 + lane;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 r4 = make_uint4(0, 0, 0, 0);
+            if (grow < M && col0 + 8 * j < N)
+              r4 = *reinterpret_cast<const uint4*>(R + (int64_t)grow * ldr + col0 + 8 * j);
+            uint32_t(&dst)[32] = j < 4 ? v : w;
+            const int o = (j & 3) * 8;
+            float lo, hi;
+            unpack2<BF16>(r4.x, lo, hi);
+            dst[o + 0] = __float_as_uint(__uint_as_float(dst[o + 0]) + lo);
+            dst[o + 1] = __float_as_uint(__uint_as_float(dst[o + 1]) + hi);
+            unpack2<BF16>(r4.y, lo, hi);
+            dst[o + 2] = __float_as_uint(__uint_as_float(dst[o + 2]) + lo);
+            dst[o + 3] = __float_as_uint(__uint_as_float(dst[o + 3]) + hi);
+            unpack2<BF16>(r4.z, lo, hi);
+            dst[o + 4] = __float_as_uint(__uint_as_float(dst[o + 4]) + lo);
+            dst[o + 5] = __float_as_uint(__uint_as_float(dst[o + 5]) + hi);
+            unpack2<BF16>(r4.w, lo, hi);
+            dst[o + 6] = __float_as_uint(__uint_as_float(dst[o + 6]) + lo);
+            dst[o + 7] = __float_as_uint(__uint_as_float(dst[o + 7]) + hi);
+          }
+        }
         if (lane == 0) tma_store_wait_read<1>();  // the store that last read `buf` has drained
         __syncwarp();
-        uint8_t* rowp = buf + lane * 128;
+        if constexpr (EPI == kEpiSwiglu) {
+          // 64 accumulator columns = 32 (gate, up) pairs -> 32 outputs = 64 bytes per row; rows of
+          // 64 bytes under the 64-byte swizzle: 16-byte chunk g of row r sits at g ^ ((r >> 1) & 3)
+          uint8_t* rowp = buf + lane * 64;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 q;
-          q.x = pack2<BF16>(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
-          q.y = pack2<BF16>(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
-          q.z = pack2<BF16>(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
-          q.w = pack2<BF16>(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
-          *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = q;
-        }
+          for (int g4 = 0; g4 < 4; ++g4) {
+            const uint32_t(&src)[32] = g4 < 2 ? v : w;
+            const int o = (g4 & 1) * 16;
+            uint4 q;
+            q.x = pack2<BF16>(silu_mul(__uint_as_float(src[o + 0]), __uint_as_float(src[o + 1])),
+                              silu_mul(__uint_as_float(src[o + 2]), __uint_as_float(src[o + 3])));
+            q.y = pack2<BF16>(silu_mul(__uint_as_float(src[o + 4]), __uint_as_float(src[o + 5])),
+                              silu_mul(__uint_as_float(src[o + 6]), __uint_as_float(src[o + 7])));
+            q.z = pack2<BF16>(silu_mul(__uint_as_float(src[o + 8]), __uint_as_float(src[o + 9])),
+                              silu_mul(__uint_as_float(src[o + 10]), __uint_as_float(src[o + 11])));
+            q.w = pack2<BF16>(silu_mul(__uint_as_float(src[o + 12]), __uint_as_float(src[o + 13])),
+                              silu_mul(__uint_as_float(src[o + 14]), __uint_as_float(src[o + 15])));
+            *reinterpret_cast<uint4*>(rowp + ((g4 ^ ((lane >> 1) & 3)) << 4)) = q;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row0 < M && col0 < N) {
+            for (int d = 0; d < num_dst; ++d) tma_store_2d(&tmC.m[d], buf, col0 / 2, row0);
+            tma_store_commit();
+          }
+        } else {
+          uint8_t* rowp = buf + lane * 128;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 q;
-          q.x = pack2<BF16>(__uint_as_float(w[8 * j + 0]), __uint_as_float(w[8 * j + 1]));
-          q.y = pack2<BF16>(__uint_as_float(w[8 * j + 2]), __uint_as_float(w[8 * j + 3]));
-          q.z = pack2<BF16>(__uint_as_float(w[8 * j + 4]), __uint_as_float(w[8 * j + 5]));
-          q.w = pack2<BF16>(__uint_as_float(w[8 * j + 6]), __uint_as_float(w[8 * j + 7]));
-          *reinterpret_cast<uint4*>(rowp + (((j + 4) ^ (lane & 7)) << 4)) = q;
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        const int col0 = nb * BN + c * 64;
-        if (lane == 0 && row0 < M && col0 < N) {
-          for (int d = 0; d < num_dst; ++d) tma_store_2d(&tmC.m[d], buf, col0, row0);
-          tma_store_commit();
+          for (int j = 0; j < 4; ++j) {
+            uint4 q;
+            q.x = pack2<BF16>(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+            q.y = pack2<BF16>(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+            q.z = pack2<BF16>(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+            q.w = pack2<BF16>(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+            *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = q;
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 q;
+            q.x = pack2<BF16>(__uint_as_float(w[8 * j + 0]), __uint_as_float(w[8 * j + 1]));
+            q.y = pack2<BF16>(__uint_as_float(w[8 * j + 2]), __uint_as_float(w[8 * j + 3]));
+            q.z = pack2<BF16>(__uint_as_float(w[8 * j + 4]), __uint_as_float(w[8 * j + 5]));
+            q.w = pack2<BF16>(__uint_as_float(w[8 * j + 6]), __uint_as_float(w[8 * j + 7]));
+            *reinterpret_cast<uint4*>(rowp + (((j + 4) ^ (lane & 7)) << 4)) = q;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row0 < M && col0 < N) {
+            for (int d = 0; d < num_dst; ++d) tma_store_2d(&tmC.m[d], buf, col0, row0);
+            tma_store_commit();
+          }
         }
       }
       tc_fence_before();
@@ -357,11 +432,11 @@ gemm_generic_kernel(const void* __restrict__ A, const void* __restrict__ B, void
   }
 }
 
-template <int CTAS, int BN, int STAGES, bool BF16>
+template <int CTAS, int BN, int STAGES, bool BF16, int EPI = kEpiNone>
 int launch_tc(const void* A, const void* B, void* const* Cs, int num_dst, int M, int N, int K, int64_t lda,
-              int64_t ldb, int64_t ldc, cudaStream_t stream) {
+              int64_t ldb, int64_t ldc, cudaStream_t stream, const void* R = nullptr, int64_t ldr = 0) {
   using L = GemmSmem<CTAS, BN, STAGES>;
-  auto kfn = gemm_tc_kernel<CTAS, BN, STAGES, BF16>;
+  auto kfn = gemm_tc_kernel<CTAS, BN, STAGES, BF16, EPI>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -378,22 +453,23 @@ int launch_tc(const void* A, const void* B, void* const* Cs, int num_dst, int M,
     uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
     uint64_t str[1] = {(uint64_t)lda * 2};
     uint32_t box[2] = {kBK, kBM};
-    int r = encode_tmap_16bit(&tmA, A, 2, dims, str, box, true);
+    int r = encode_tmap_16bit(&tmA, A, 2, dims, str, box, 1);
     if (r) return r;
   }
   {
     uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
     uint64_t str[1] = {(uint64_t)ldb * 2};
     uint32_t box[2] = {64, kBK};
-    int r = encode_tmap_16bit(&tmB, B, 2, dims, str, box, true);
+    int r = encode_tmap_16bit(&tmB, B, 2, dims, str, box, 1);
     if (r) return r;
   }
   for (int d = 0; d < kMaxDst; ++d) {
     // unused slots repeat the first map so that the parameter block holds no garbage
-    uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
+    // the SwiGLU epilogue writes N/2 columns, 32 per chunk (64-byte rows, 64-byte swizzle)
+    uint64_t dims[2] = {(uint64_t)(EPI == kEpiSwiglu ? N / 2 : N), (uint64_t)M};
     uint64_t str[1] = {(uint64_t)ldc * 2};
-    uint32_t box[2] = {64, 32};
-    int r = encode_tmap_16bit(&tmC.m[d], Cs[d < num_dst ? d : 0], 2, dims, str, box, true);
+    uint32_t box[2] = {EPI == kEpiSwiglu ? 32u : 64u, 32};
+    int r = encode_tmap_16bit(&tmC.m[d], Cs[d < num_dst ? d : 0], 2, dims, str, box, EPI == kEpiSwiglu ? 2 : 1);
     if (r) return r;
   }
   int* status = status_ptr();
@@ -413,7 +489,8 @@ int launch_tc(const void* A, const void* B, void* const* Cs, int num_dst, int M,
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kfn, tmA, tmB, tmC, num_dst, M, N, K, status);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kfn, tmA, tmB, tmC, num_dst, M, N, K, status,
+                                     reinterpret_cast<const uint16_t*>(R), ldr);
   count_launch();
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
@@ -516,4 +593,34 @@ extern "C" int b200k_gemm_scatter(const void* A, const void* B, void* const* C_d
                 : launch_tc<2, 256, 6, false>(A, B, C_dsts, num_dst, M, N, K, lda, ldb, ldc, stream);
   return bf16 ? launch_tc<1, 128, 6, true>(A, B, C_dsts, num_dst, M, N, K, lda, ldb, ldc, stream)
               : launch_tc<1, 128, 6, false>(A, B, C_dsts, num_dst, M, N, K, lda, ldb, ldc, stream);
+}
+
+extern "C" int b200k_gemm_fused(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int64_t lda,
+                                int64_t ldb, int64_t ldc, int64_t ldr, int dtype, int epilogue,
+                                b200k_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (dtype != B200K_F16 && dtype != B200K_BF16) return B200K_EDTYPE;
+  if (epilogue != B200K_EPI_ADD && epilogue != B200K_EPI_SWIGLU) return B200K_EARG;
+  const int n_out = epilogue == B200K_EPI_SWIGLU ? N / 2 : N;
+  if (M <= 0 || N <= 0 || K <= 0 || lda < K || ldb < N || ldc < n_out) return B200K_ESHAPE;
+  if (epilogue == B200K_EPI_SWIGLU && N % 16 != 0) return B200K_ESHAPE;  // pairs, and 16-byte output chunks
+  if (!A || !B || !C) return B200K_EARG;
+  if (!aligned16(A) || !aligned16(B) || !aligned16(C) || lda % 8 || ldb % 8 || ldc % 8) return B200K_EALIGN;
+  if (epilogue == B200K_EPI_ADD) {
+    if (!R) return B200K_EARG;
+    if (ldr < N) return B200K_ESHAPE;
+    if (!aligned16(R) || ldr % 8) return B200K_EALIGN;
+  }
+  if (!b200k_device_supported()) return B200K_ENOGPU;
+  const int sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
+  const long pair_tiles = (long)((M + 255) / 256) * ((N + 255) / 256);
+  const bool big = pair_tiles >= sms / 2;
+  const bool bf16 = dtype == B200K_BF16;
+#define B200K_FUSED(EP)                                                                                       \
+  (big ? (bf16 ? launch_tc<2, 256, 6, true, EP>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream, R, ldr)         \
+               : launch_tc<2, 256, 6, false, EP>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream, R, ldr))       \
+       : (bf16 ? launch_tc<1, 128, 6, true, EP>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream, R, ldr)         \
+               : launch_tc<1, 128, 6, false, EP>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream, R, ldr)))
+  return epilogue == B200K_EPI_ADD ? B200K_FUSED(kEpiAdd) : B200K_FUSED(kEpiSwiglu);
+#undef B200K_FUSED
 }

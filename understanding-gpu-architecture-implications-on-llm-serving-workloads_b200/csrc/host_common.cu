@@ -41,7 +41,7 @@ namespace {
 struct TmapKey {
   const void* base;
   int rank;
-  bool swizzle;
+  int swizzle;
   uint64_t dims[4];
   uint64_t strides[3];
   uint32_t box[4];
@@ -67,14 +67,14 @@ TmapCache& tmap_cache() {
 }  // namespace
 
 int encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                      const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
+                      const uint64_t* strides_bytes, const uint32_t* box, int swizzle) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return B200K_ECUDA;
   if (rank < 1 || rank > 4) return B200K_ETMAP;
   TmapKey key{};
   key.base = base;
   key.rank = rank;
-  key.swizzle = swizzle128;
+  key.swizzle = swizzle;
   for (int i = 0; i < rank; ++i) {
     key.dims[i] = dims[i];
     key.box[i] = box[i];
@@ -103,7 +103,9 @@ int encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64
   // interpreted; both tile 2-byte elements and the fill used here is zero.
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdims, gstrides,
                   gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B
+                  : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                 : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return B200K_ETMAP;
   {

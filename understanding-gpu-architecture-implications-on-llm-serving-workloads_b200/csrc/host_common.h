@@ -13,9 +13,9 @@ namespace b200k {
 
 // 16-bit element tensor map.  dims/strides innermost first; strides_bytes[i] is
 // the byte stride of dimension i+1 (dimension 0 is contiguous).
-// Returns B200K_OK / B200K_ETMAP / B200K_ECUDA.
+// swizzle: 0 = none, 1 = 128-byte, 2 = 64-byte.  Returns B200K_OK / B200K_ETMAP / B200K_ECUDA.
 int encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                      const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128);
+                      const uint64_t* strides_bytes, const uint32_t* box, int swizzle);
 
 // Device pointer to the int[4] status word of the current device.
 int* status_ptr();
