@@ -162,3 +162,17 @@ def test_reference_wrapper_semantics(cuda_device):
         fmha_unified.ops.fine_fmha(q, k, v, True, False, 6)      # declared, not implemented
     with pytest.raises(RuntimeError):
         fmha_unified.ops.fine_fmha(q.float(), k.float(), v.float(), True, False, 0)
+
+
+@pytest.mark.parametrize("variant", [1, 2, 3, 11, 12, 13])
+def test_kernel_variants_agree(cuda_device, variant):
+    """One-item-per-CTA and persistent kernels, with 0, 1 or 2 of every 4 exponentials on the FMA pipe:
+    all within tolerance of the oracle, causal with ragged length and GQA."""
+    from b200k import fmha, inputs
+    q, k, v = inputs.fmha_inputs(2, 8, 2, 700, 700, 128, torch.float16, seed=44)
+    o = fmha.fmha_fwd(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), causal=True, variant=variant)
+    assert oracle.max_abs(o, oracle.fmha_ref(q, k, v, causal=True)) <= TOL
+    q, k, v = inputs.fmha_inputs(3, 4, 4, 130, 5000, 64, torch.bfloat16, seed=45)
+    o = fmha.fmha_fwd(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), causal=False, variant=variant)
+    ref = oracle.fmha_ref(q, k, v)
+    assert oracle.max_abs(o, ref) <= _tol(torch.bfloat16, ref)

@@ -28,6 +28,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math.h>
+#include <stdlib.h>
 
 #include "host_common.h"
 #include "ptx.cuh"
@@ -518,6 +519,462 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Persistent variant: one CTA per SM walks a list of work items (batch, head, tile pair).  TMEM,
+// barriers and tensor-map prefetches are set up once; the K/V rings, the S/P handshakes and the
+// Q / O hand-overs keep running across items (every barrier's phase is tracked with a running
+// counter), so the loads and the first QK^T of the next item overlap the last PV and the epilogue
+// of the current one.  The epilogue stages O in its own 16 KB buffer per warpgroup (64 columns at a
+// time) instead of the Q tile, which the loader may already be refilling.
+// ---------------------------------------------------------------------------------------------
+template <int D>
+struct FmhaPSmem {
+  static constexpr uint32_t kTileBytes = kTile * D * 2;
+  static constexpr uint32_t kHalfBytes = kTile * 128;
+  static constexpr uint32_t kQOff = 0;
+  static constexpr uint32_t kKOff = 2 * kTileBytes;
+  static constexpr uint32_t kVOff = 4 * kTileBytes;
+  static constexpr uint32_t kStageOff = 6 * kTileBytes;        // 2 x 16 KB output staging
+  static constexpr uint32_t kBarOff = kStageOff + 2 * kHalfBytes;
+  static constexpr uint32_t kTotal = kBarOff + 256 + 1024;
+};
+
+struct FmhaItem {
+  int h, b, hk;
+  int q0[2], nb[2];
+  bool valid[2];
+  int nb_max;
+};
+
+__device__ __forceinline__ FmhaItem fmha_item(const FmhaParams& p, int idx) {
+  FmhaItem it;
+  int pair;
+  if (p.head_major) {
+    pair = p.num_pairs - 1 - idx % p.num_pairs;
+    const int t = idx / p.num_pairs;
+    it.h = t % p.Hq;
+    it.b = t / p.Hq;
+  } else {
+    it.h = idx % p.Hq;
+    const int t = idx / p.Hq;
+    it.b = t % p.B;
+    pair = p.num_pairs - 1 - t / p.B;
+  }
+  it.hk = it.h / (p.Hq / p.Hkv);
+  const int off = p.kv_len - p.Sq;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    it.q0[i] = (pair * 2 + i) * kTile;
+    it.valid[i] = it.q0[i] < p.Sq;
+    int kv_hi = p.kv_len;
+    if (p.causal) {
+      const int last_row = min(it.q0[i] + kTile, p.Sq) - 1;
+      kv_hi = max(0, min(p.kv_len, last_row + off + 1));
+    }
+    it.nb[i] = it.valid[i] ? (kv_hi + kTile - 1) / kTile : 0;
+  }
+  it.nb_max = max(it.nb[0], it.nb[1]);
+  return it;
+}
+
+template <int D, bool BF16, int EMU>
+__global__ void __launch_bounds__(kFmhaThreads, 1)
+fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                           const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                           const FmhaParams p, int total_items) {
+  using L = FmhaPSmem<D>;
+  constexpr int kDBoxes = D / 64;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kSCol0 = 0, kSCol1 = 128, kOCol0 = 256, kOCol1 = 256 + D;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* q_full = bars;         // [2]  Q_i landed
+  uint64_t* q_free = bars + 2;     // [2]  every S MMA of the item has read Q_i
+  uint64_t* k_full = bars + 4;     // [2]
+  uint64_t* k_empty = bars + 6;    // [2]
+  uint64_t* v_full = bars + 8;     // [2]
+  uint64_t* v_empty = bars + 10;   // [2]
+  uint64_t* s_full = bars + 12;    // [2]
+  uint64_t* p_ready = bars + 14;   // [2]
+  uint64_t* o_full = bars + 16;    // [2]  last PV of the item done
+  uint64_t* o_free = bars + 18;    // [2]  epilogue has read O_i out of TMEM
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 20);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  // Items are ordered heavy to light; round r hands items [r*G, (r+1)*G) to the G CTAs forwards on
+  // even rounds and backwards on odd ones, which evens out linearly decreasing work.
+  auto snake_item = [&](int r) {
+    const int g = (int)gridDim.x;
+    return r * g + ((r & 1) ? g - 1 - (int)blockIdx.x : (int)blockIdx.x);
+  };
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_free[i], 1);
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_ready[i], 128);
+      mbar_init(&o_full[i], 1);
+      mbar_init(&o_free[i], 128);
+    }
+    fence_mbar_init();
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+    prefetch_tmap(&tmO);
+  }
+  if (warp == 9) {
+    tmem_alloc<1>(tmem_holder, kTmemCols);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp >= 10) {
+    reg_dealloc<56>();
+  } else if (warp == 8) {
+    // ------------------------------- TMA loader -------------------------------
+    reg_dealloc<56>();
+    if (elect_one()) {
+      uint32_t kc = 0, vc = 0, qn[2] = {0, 0};
+      bool ok = true;
+      auto load_tile = [&](const CUtensorMap* tm, uint8_t* dst, uint64_t* bar, int row, int head, int b) {
+        mbar_expect_tx(bar, L::kTileBytes);
+#pragma unroll
+        for (int d = 0; d < kDBoxes; ++d) tma_load_4d(dst + d * L::kHalfBytes, tm, bar, d * 64, row, head, b);
+      };
+      auto load_k = [&](const FmhaItem& it, int j) {
+        const uint32_t st = kc & 1;
+        if (!mbar_wait(&k_empty[st], ((kc >> 1) & 1) ^ 1)) {
+          report_timeout(p.status, KID_FMHA, ROLE_PRODUCER);
+          ok = false;
+          return;
+        }
+        load_tile(&tmK, smem + L::kKOff + st * L::kTileBytes, &k_full[st], j * kTile, it.hk, it.b);
+        ++kc;
+      };
+      for (int r = 0; r * (int)gridDim.x < total_items && ok; ++r) {
+        const int w = snake_item(r);
+        if (w >= total_items) continue;
+        const FmhaItem it = fmha_item(p, w);
+        if (it.nb_max == 0) continue;
+        load_k(it, 0);
+        for (int i = 0; i < 2 && ok; ++i) {
+          if (it.nb[i] == 0) continue;
+          if (!mbar_wait(&q_free[i], (qn[i] & 1) ^ 1)) {
+            report_timeout(p.status, KID_FMHA, ROLE_PRODUCER);
+            ok = false;
+            break;
+          }
+          load_tile(&tmQ, smem + L::kQOff + i * L::kTileBytes, &q_full[i], it.q0[i], it.h, it.b);
+          ++qn[i];
+        }
+        for (int j = 0; j < it.nb_max && ok; ++j) {
+          const uint32_t st = vc & 1;
+          if (!mbar_wait(&v_empty[st], ((vc >> 1) & 1) ^ 1)) {
+            report_timeout(p.status, KID_FMHA, ROLE_PRODUCER);
+            ok = false;
+            break;
+          }
+          load_tile(&tmV, smem + L::kVOff + st * L::kTileBytes, &v_full[st], j * kTile, it.hk, it.b);
+          ++vc;
+          if (j + 1 < it.nb_max) load_k(it, j + 1);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------- MMA issuer -------------------------------
+    reg_dealloc<56>();
+    if (elect_one()) {
+      constexpr uint32_t idesc_s = make_idesc_f16(BF16 ? 1 : 0, 0, 0, kTile, kTile);
+      constexpr uint32_t idesc_pv = make_idesc_f16(BF16 ? 1 : 0, 0, 1, kTile, D);
+      const uint32_t q_addr = smem_u32(smem + L::kQOff);
+      const uint32_t k_addr = smem_u32(smem + L::kKOff);
+      const uint32_t v_addr = smem_u32(smem + L::kVOff);
+      const uint32_t s_col[2] = {kSCol0, kSCol1};
+      const uint32_t o_col[2] = {kOCol0, kOCol1};
+      uint32_t kc = 0, vc = 0, qn[2] = {0, 0}, pn[2] = {0, 0}, on[2] = {0, 0};
+      bool ok = true;
+      auto fail = [&]() {
+        report_timeout(p.status, KID_FMHA, ROLE_MMA);
+        ok = false;
+      };
+      auto issue_s = [&](int i, uint32_t stage) {
+        const uint32_t qa = q_addr + i * L::kTileBytes;
+        const uint32_t ka = k_addr + stage * L::kTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t o = (kk >> 2) * L::kHalfBytes + (kk & 3) * 32;
+          umma_ss<1>(tmem_base + s_col[i], make_smem_desc_sw128(qa + o, 16, 1024),
+                     make_smem_desc_sw128(ka + o, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit<1>(&s_full[i]);
+      };
+      auto issue_pv = [&](int i, uint32_t stage, bool first) {
+        const uint32_t va = v_addr + stage * L::kTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk) {
+          umma_ts(tmem_base + o_col[i], tmem_base + s_col[i] + kk * 8,
+                  make_smem_desc_sw128(va + kk * 2048, L::kHalfBytes, 1024), idesc_pv,
+                  (!first || kk > 0) ? 1u : 0u);
+        }
+      };
+      for (int r = 0; r * (int)gridDim.x < total_items && ok; ++r) {
+        const int w = snake_item(r);
+        if (w >= total_items) continue;
+        const FmhaItem it = fmha_item(p, w);
+        if (it.nb_max == 0) continue;
+        // first score block of both tiles
+        if (!mbar_wait(&k_full[kc & 1], (kc >> 1) & 1)) {
+          fail();
+          break;
+        }
+        for (int i = 0; i < 2 && ok; ++i) {
+          if (it.nb[i] == 0) continue;
+          if (!mbar_wait(&q_full[i], qn[i] & 1)) {
+            fail();
+            break;
+          }
+          tc_fence_after();
+          issue_s(i, kc & 1);
+        }
+        if (!ok) break;
+        umma_commit<1>(&k_empty[kc & 1]);
+        ++kc;
+        for (int j = 0; j < it.nb_max && ok; ++j) {
+          if (!mbar_wait(&v_full[vc & 1], (vc >> 1) & 1)) {
+            fail();
+            break;
+          }
+          bool k_next_ready = false;
+          for (int i = 0; i < 2 && ok; ++i) {
+            if (j >= it.nb[i]) continue;
+            if (!mbar_wait(&p_ready[i], pn[i] & 1)) {
+              fail();
+              break;
+            }
+            ++pn[i];
+            if (j == 0 && !mbar_wait(&o_free[i], (on[i] & 1) ^ 1)) {  // previous item's O_i was read out
+              fail();
+              break;
+            }
+            tc_fence_after();
+            issue_pv(i, vc & 1, j == 0);
+            if (j == it.nb[i] - 1) {
+              umma_commit<1>(&o_full[i]);
+              ++on[i];
+              umma_commit<1>(&q_free[i]);  // covers the item's last S_i as well
+              ++qn[i];
+            }
+            if (j + 1 < it.nb[i]) {
+              if (!k_next_ready) {
+                if (!mbar_wait(&k_full[kc & 1], (kc >> 1) & 1)) {
+                  fail();
+                  break;
+                }
+                tc_fence_after();
+                k_next_ready = true;
+              }
+              issue_s(i, kc & 1);
+            }
+          }
+          if (!ok) break;
+          umma_commit<1>(&v_empty[vc & 1]);
+          ++vc;
+          if (j + 1 < it.nb_max) {
+            umma_commit<1>(&k_empty[kc & 1]);
+            ++kc;
+          }
+        }
+      }
+    }
+  } else {
+    // ----------------------------- softmax groups -----------------------------
+    reg_alloc<224>();
+    const int i = warp >> 2;
+    const int row = threadIdx.x & 127;
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t s_tmem = tmem_base + lane_sel + (i == 0 ? kSCol0 : kSCol1);
+    const uint32_t o_tmem = tmem_base + lane_sel + (i == 0 ? kOCol0 : kOCol1);
+    uint8_t* stage = smem + L::kStageOff + i * L::kHalfBytes;
+    const float sc = p.scale_log2;
+    const int off = p.kv_len - p.Sq;
+    uint32_t sn = 0, itn = 0;
+    bool ok = true;
+    bool store_pending = false;
+    for (int r = 0; r * (int)gridDim.x < total_items && ok; ++r) {
+      const int w = snake_item(r);
+      if (w >= total_items) continue;
+      const FmhaItem it = fmha_item(p, w);
+      if (!it.valid[i]) continue;
+      const int q = it.q0[i] + row;
+      const int lim_row = p.causal ? min(q + off, p.kv_len - 1) : p.kv_len - 1;
+      const int tile_min_lim = p.causal ? min(it.q0[i] + off, p.kv_len - 1) : p.kv_len - 1;
+      float m_use = -INFINITY;
+      float l = 0.f;
+      for (int j = 0; j < it.nb[i]; ++j) {
+        if (!mbar_wait(&s_full[i], sn & 1)) {
+          if (lane == 0) report_timeout(p.status, KID_FMHA, ROLE_SOFTMAX);
+          ok = false;
+          break;
+        }
+        ++sn;
+        tc_fence_after();
+        uint32_t s[128];
+        tmem_ld32(s_tmem + 0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        tmem_ld32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+        tmem_ld32(s_tmem + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
+        tmem_ld32(s_tmem + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
+        tmem_ld_wait();
+        const int k0 = j * kTile;
+        if (k0 + kTile - 1 > tile_min_lim) {
+          const int lim = lim_row - k0;
+#pragma unroll
+          for (int k = 0; k < 128; ++k)
+            if (k > lim) s[k] = 0xff800000u;
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < 128; k += 8) {
+          mx0 = max3(mx0, __uint_as_float(s[k + 0]), __uint_as_float(s[k + 1]));
+          mx1 = max3(mx1, __uint_as_float(s[k + 2]), __uint_as_float(s[k + 3]));
+          mx2 = max3(mx2, __uint_as_float(s[k + 4]), __uint_as_float(s[k + 5]));
+          mx3 = max3(mx3, __uint_as_float(s[k + 6]), __uint_as_float(s[k + 7]));
+        }
+        const float m_new = fmaxf(m_use, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc);
+        if (j == 0) {
+          m_use = m_new;
+        } else {
+          const bool need = (m_new - m_use) > kRescaleThreshold;
+          if (__any_sync(0xffffffffu, need)) {
+            const float f = (m_new == -INFINITY) ? 1.f : ex2(m_use - m_new);
+            m_use = m_new;
+            l *= f;
+            const uint64_t f2 = f2pack(f, f);
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld32(o_tmem + c * 32, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 32; e += 2) {
+                float a, bb;
+                f2unpack(mul2(f2pack(__uint_as_float(o[e]), __uint_as_float(o[e + 1])), f2), a, bb);
+                o[e] = __float_as_uint(a);
+                o[e + 1] = __float_as_uint(bb);
+              }
+              tmem_st32(o_tmem + c * 32, o);
+            }
+          }
+        }
+        const float neg = (m_use == -INFINITY) ? 0.f : -m_use;
+        const uint64_t sc2 = f2pack(sc, sc), neg2 = f2pack(neg, neg);
+        uint64_t sum_a = f2pack(0.f, 0.f), sum_b = f2pack(0.f, 0.f);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int k = c * 64 + (e + g) * 2;
+              const uint64_t x2 = fma2(f2pack(__uint_as_float(s[k]), __uint_as_float(s[k + 1])), sc2, neg2);
+              float p0, p1;
+              if (g >= 4 - EMU) {
+                ex2_emulated(x2, p0, p1);
+              } else {
+                float x0, x1;
+                f2unpack(x2, x0, x1);
+                p0 = ex2(x0);
+                p1 = ex2(x1);
+              }
+              if (g & 1)
+                sum_b = add2(sum_b, f2pack(p0, p1));
+              else
+                sum_a = add2(sum_a, f2pack(p0, p1));
+              pk[e + g] = pack16<BF16>(p0, p1);
+            }
+          }
+          tmem_st32(s_tmem + c * 32, pk);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&p_ready[i]);
+        {
+          float a, bb;
+          f2unpack(add2(sum_a, sum_b), a, bb);
+          l += a + bb;
+        }
+      }
+      if (!ok) break;
+
+      // ------------------------------ epilogue ------------------------------
+      uint32_t o[D];
+      if (it.nb[i] > 0) {
+        if (!mbar_wait(&o_full[i], itn & 1)) {
+          if (lane == 0) report_timeout(p.status, KID_FMHA, ROLE_EPILOGUE);
+          ok = false;
+          break;
+        }
+        ++itn;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tmem_ld32(o_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&o[c * 32]));
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(&o_free[i]);  // the next item's first PV may overwrite O_i now
+      } else {
+#pragma unroll
+        for (int e = 0; e < D; ++e) o[e] = 0u;
+      }
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+      for (int hb = 0; hb < kDBoxes; ++hb) {
+        // the previous TMA store out of this staging buffer must have finished reading it
+        if (store_pending) {
+          if (row == 0) tma_store_wait_read<0>();
+          named_barrier_sync(1 + i, 128);
+        }
+        uint8_t* rowp = stage + row * 128;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const int e = hb * 64 + g * 8;
+          uint4 wv;
+          wv.x = pack16<BF16>(__uint_as_float(o[e + 0]) * inv, __uint_as_float(o[e + 1]) * inv);
+          wv.y = pack16<BF16>(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
+          wv.z = pack16<BF16>(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
+          wv.w = pack16<BF16>(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
+          *reinterpret_cast<uint4*>(rowp + ((g ^ (row & 7)) << 4)) = wv;
+        }
+        fence_proxy_async_smem();
+        named_barrier_sync(1 + i, 128);
+        if (row == 0) {
+          tma_store_4d(&tmO, stage, hb * 64, it.q0[i], it.h, it.b);
+          tma_store_commit();
+        }
+        store_pending = true;
+      }
+    }
+    if (row == 0) tma_store_wait_all<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, kTmemCols);
+  }
+}
+
 int make_map_bhsd(CUtensorMap* tm, const void* base, int D, int S, int H, int B, const int64_t st[3]) {
   uint64_t dims[4] = {(uint64_t)D, (uint64_t)S, (uint64_t)H, (uint64_t)B};
   uint64_t strides[3] = {(uint64_t)st[2] * 2, (uint64_t)st[1] * 2, (uint64_t)st[0] * 2};
@@ -528,14 +985,17 @@ int make_map_bhsd(CUtensorMap* tm, const void* base, int D, int S, int H, int B,
 template <int D, bool BF16, int EMU>
 int launch_fmha(const void* Q, const void* K, const void* V, void* O, int B, int Hq, int Hkv, int Sq, int kv_len,
                 const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, float scale, int causal,
-                cudaStream_t stream) {
+                bool persistent, cudaStream_t stream) {
   using L = FmhaSmem<D>;
+  using LP = FmhaPSmem<D>;
   auto kfn = fmha_fwd_kernel<D, BF16, EMU>;
+  auto kfn_p = fmha_fwd_persistent_kernel<D, BF16, EMU>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!configured[dev & 63]) {
-    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal) != cudaSuccess) {
+    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal) != cudaSuccess ||
+        cudaFuncSetAttribute(kfn_p, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LP::kTotal) != cudaSuccess) {
       (void)cudaGetLastError();
       return B200K_ECUDA;
     }
@@ -563,7 +1023,13 @@ int launch_fmha(const void* Q, const void* K, const void* V, void* O, int B, int
   if (!p.status) return B200K_ECUDA;
   const long grid = (long)p.num_pairs * Hq * B;
   if (grid <= 0 || grid > 0x7fffffffL) return B200K_ESHAPE;
-  kfn<<<(unsigned)grid, kFmhaThreads, L::kTotal, stream>>>(tmQ, tmK, tmV, tmO, p);
+  if (persistent) {
+    const int sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
+    const unsigned ctas = (unsigned)(grid < sms ? grid : sms);
+    kfn_p<<<ctas, kFmhaThreads, LP::kTotal, stream>>>(tmQ, tmK, tmV, tmO, p, (int)grid);
+  } else {
+    kfn<<<(unsigned)grid, kFmhaThreads, L::kTotal, stream>>>(tmQ, tmK, tmV, tmO, p);
+  }
   count_launch();
   return check_launch();
 }
@@ -596,11 +1062,21 @@ extern "C" int b200k_fmha_fwd(const void* Q, const void* K, const void* V, void*
   const bool bf16 = dtype == B200K_BF16;
   // variant: 0 = default; 1, 2, 3 = 0, 1, 2 of every 4 score pairs take their exponential on the
   // FMA pipe instead of the MUFU (kept selectable for ablation)
-  const int emu = variant == 0 ? kDefaultEmu : variant - 1;
+  // 11, 12, 13 = the same three with the persistent kernel
+  // Default: the persistent kernel for kv_len <= 4096 (measured +3 % at 4096, +10 % at 2048, +19..31 %
+  // at 1024, where per-CTA set-up weighs most), the one-item-per-CTA kernel beyond (measured 5-7 %
+  // ahead at 8192 / 16384, where the hardware's dynamic CTA scheduling balances better than the static
+  // item lists).  B200K_FMHA_PERSISTENT=0/1 overrides.
+  static const int env_persistent = [] {
+    const char* e = getenv("B200K_FMHA_PERSISTENT");
+    return e ? (e[0] == '1' ? 1 : 0) : -1;
+  }();
+  const bool persistent = variant != 0 ? variant >= 10 : env_persistent >= 0 ? env_persistent == 1 : kv_len <= 4096;
+  const int emu = variant == 0 ? kDefaultEmu : (variant % 10) - 1;
   if (emu < 0 || emu > 2) return B200K_EARG;
 #define B200K_FMHA(DD, BF, EM)                                                                                  \
   launch_fmha<DD, BF, EM>(Q, K, V, O, B, Hq, Hkv, Sq, kv_len, q_strides, k_strides, v_strides, o_strides, scale, \
-                          causal, stream)
+                          causal, persistent, stream)
 #define B200K_FMHA_EMU(DD, BF) (emu == 0 ? B200K_FMHA(DD, BF, 0) : emu == 1 ? B200K_FMHA(DD, BF, 1) : B200K_FMHA(DD, BF, 2))
   if (D == 128) return bf16 ? B200K_FMHA_EMU(128, true) : B200K_FMHA_EMU(128, false);
   return bf16 ? B200K_FMHA_EMU(64, true) : B200K_FMHA_EMU(64, false);
