@@ -47,7 +47,7 @@ enum {
   B200K_GEMM_AUTO = 0,      /* heuristic: picks one of the below from M, N, K */
   B200K_GEMM_1CTA = 1,      /* 128x256x64 tiles, one CTA per tile, persistent, warp-specialised */
   B200K_GEMM_2CTA = 2,      /* 256x256x64 tiles on a CTA pair (cta_group::2) */
-  B200K_GEMM_SKINNY = 3,    /* M <= 128: weight-streaming split-K path */
+  B200K_GEMM_SKINNY = 3,    /* M <= 128: weight streaming, split-K inside thread-block clusters */
   B200K_GEMM_1CTA_N128 = 4, /* 128x128x64 tiles: more CTAs for small problems */
   B200K_GEMM_GENERIC = 5    /* CUDA-core kernel without alignment rules (any M, N, K, ld) */
 };
@@ -63,8 +63,9 @@ enum {
  * contract is a[i*K+k], b[k*N+j], c[i*N+j] (auto/gemm_0.cu:12-20).
  * The tensor-core variants need 16-byte aligned bases and lda, ldb, ldc
  * multiples of 8 elements; AUTO falls back to GENERIC otherwise.
- * `workspace` is only used by B200K_GEMM_SKINNY (split-K partial sums, see
- * b200k_gemm_workspace_bytes); it may be NULL for the other variants.
+ * No variant needs a workspace today (the split-K partial sums of B200K_GEMM_SKINNY stay in
+ * distributed shared memory): `workspace` may be NULL; the arguments are kept so that a
+ * future variant can use one without changing the ABI.
  */
 int b200k_gemm(const void* A_device, const void* B_device, void* C_device,
                int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
@@ -105,7 +106,7 @@ int b200k_gemm_fused(const void* A_device, const void* B_device, void* C_device,
                      int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr,
                      int dtype, int epilogue, b200k_stream_t stream);
 
-/* Bytes of workspace b200k_gemm needs for (M,N,K,variant); 0 when none. */
+/* Bytes of workspace b200k_gemm needs for (M,N,K,variant); 0 for every current variant. */
 size_t b200k_gemm_workspace_bytes(int M, int N, int K, int variant);
 
 /*
