@@ -39,7 +39,13 @@ namespace {
 constexpr int kFmhaThreads = 384;  // 2 softmax warpgroups + 1 warpgroup holding the TMA and MMA warps
 constexpr int kTile = 128;  // query rows per tile and keys per block
 constexpr float kRescaleThreshold = 8.0f;
-constexpr int kDefaultEmu = 1;  // of every 4 score pairs, how many exponentials run on the FMA pipe
+constexpr int kDefaultEmu = 1;
+#ifndef B200K_FMHA_SPLIT_P
+#define B200K_FMHA_SPLIT_P 1
+#endif
+// P is handed to the MMA warp in two halves of 64 keys, so that the first half of the PV product
+// runs while the softmax group still exponentiates the second half.
+constexpr bool kSplitP = B200K_FMHA_SPLIT_P != 0;  // of every 4 score pairs, how many exponentials run on the FMA pipe
 
 template <int D>
 struct FmhaSmem {
@@ -165,7 +171,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* s_full = bars + 10;   // [2]
   uint64_t* p_ready = bars + 12;  // [2]
   uint64_t* o_full = bars + 14;   // [2]
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* p_half = bars + 16;   // [2]  first 64 keys of P stored
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 18);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -214,6 +221,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_ready[i], 128);
+      mbar_init(&p_half[i], 128);
       mbar_init(&o_full[i], 1);
     }
     fence_mbar_init();
@@ -297,10 +305,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       };
       // O_i += P_i . V_stage : 8 steps of 16 keys; P from TMEM (8 columns of 16-bit pairs per
       // step), V MN-major: 16 keys = 16 rows of 128 bytes; 64-wide d boxes kHalfBytes apart.
-      auto issue_pv = [&](int i, int stage, bool first) {
+      auto issue_pv = [&](int i, int stage, bool first, int kk0, int kk1) {
         const uint32_t va = v_addr + stage * L::kTileBytes;
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk) {
+        for (int kk = kk0; kk < kk1; ++kk) {
           umma_ts(tmem_base + o_col[i], tmem_base + s_col[i] + kk * 8,
                   make_smem_desc_sw128(va + kk * 2048, L::kHalfBytes, 1024), idesc_pv,
                   (!first || kk > 0) ? 1u : 0u);
@@ -328,12 +336,20 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         bool k_next_ready = false;
         for (int i = 0; i < 2 && ok; ++i) {
           if (j >= nb[i]) continue;
+          if (kSplitP) {
+            if (!mbar_wait(&p_half[i], j & 1)) {
+              fail();
+              break;
+            }
+            tc_fence_after();
+            issue_pv(i, s, j == 0, 0, kTile / 32);
+          }
           if (!mbar_wait(&p_ready[i], j & 1)) {
             fail();
             break;
           }
           tc_fence_after();
-          issue_pv(i, s, j == 0);
+          issue_pv(i, s, j == 0, kSplitP ? kTile / 32 : 0, kTile / 16);
           if (j == nb[i] - 1) umma_commit<1>(&o_full[i]);
           if (j + 1 < nb[i]) {
             const int s1 = (j + 1) & 1;
@@ -455,6 +471,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             }
           }
           tmem_st32(s_tmem + c * 32, pk);
+          if (kSplitP && c == 0) {
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&p_half[i]);
+          }
         }
         tmem_st_wait();
         tc_fence_before();
@@ -600,7 +621,8 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
   uint64_t* p_ready = bars + 14;   // [2]
   uint64_t* o_full = bars + 16;    // [2]  last PV of the item done
   uint64_t* o_free = bars + 18;    // [2]  epilogue has read O_i out of TMEM
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 20);
+  uint64_t* p_half = bars + 20;    // [2]  first 64 keys of P stored
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 22);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -621,6 +643,7 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_ready[i], 128);
+      mbar_init(&p_half[i], 128);
       mbar_init(&o_full[i], 1);
       mbar_init(&o_free[i], 128);
     }
@@ -719,10 +742,10 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         }
         umma_commit<1>(&s_full[i]);
       };
-      auto issue_pv = [&](int i, uint32_t stage, bool first) {
+      auto issue_pv = [&](int i, uint32_t stage, bool first, int kk0, int kk1) {
         const uint32_t va = v_addr + stage * L::kTileBytes;
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk) {
+        for (int kk = kk0; kk < kk1; ++kk) {
           umma_ts(tmem_base + o_col[i], tmem_base + s_col[i] + kk * 8,
                   make_smem_desc_sw128(va + kk * 2048, L::kHalfBytes, 1024), idesc_pv,
                   (!first || kk > 0) ? 1u : 0u);
@@ -758,17 +781,25 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
           bool k_next_ready = false;
           for (int i = 0; i < 2 && ok; ++i) {
             if (j >= it.nb[i]) continue;
+            if (j == 0 && !mbar_wait(&o_free[i], (on[i] & 1) ^ 1)) {  // previous item's O_i was read out
+              fail();
+              break;
+            }
+            if (kSplitP) {
+              if (!mbar_wait(&p_half[i], pn[i] & 1)) {
+                fail();
+                break;
+              }
+              tc_fence_after();
+              issue_pv(i, vc & 1, j == 0, 0, kTile / 32);
+            }
             if (!mbar_wait(&p_ready[i], pn[i] & 1)) {
               fail();
               break;
             }
             ++pn[i];
-            if (j == 0 && !mbar_wait(&o_free[i], (on[i] & 1) ^ 1)) {  // previous item's O_i was read out
-              fail();
-              break;
-            }
             tc_fence_after();
-            issue_pv(i, vc & 1, j == 0);
+            issue_pv(i, vc & 1, j == 0, kSplitP ? kTile / 32 : 0, kTile / 16);
             if (j == it.nb[i] - 1) {
               umma_commit<1>(&o_full[i]);
               ++on[i];
@@ -905,6 +936,11 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
             }
           }
           tmem_st32(s_tmem + c * 32, pk);
+          if (kSplitP && c == 0) {
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&p_half[i]);
+          }
         }
         tmem_st_wait();
         tc_fence_before();
