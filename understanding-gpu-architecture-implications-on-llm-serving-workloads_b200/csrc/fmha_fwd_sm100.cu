@@ -40,12 +40,13 @@ constexpr int kFmhaThreads = 384;  // 2 softmax warpgroups + 1 warpgroup holding
 constexpr int kTile = 128;  // query rows per tile and keys per block
 constexpr float kRescaleThreshold = 8.0f;
 constexpr int kDefaultEmu = 1;
-#ifndef B200K_FMHA_SPLIT_P
-#define B200K_FMHA_SPLIT_P 1
+#ifndef B200K_FMHA_P_PARTS
+#define B200K_FMHA_P_PARTS 2
 #endif
-// P is handed to the MMA warp in two halves of 64 keys, so that the first half of the PV product
-// runs while the softmax group still exponentiates the second half.
-constexpr bool kSplitP = B200K_FMHA_SPLIT_P != 0;  // of every 4 score pairs, how many exponentials run on the FMA pipe
+// P is handed to the MMA warp in kPParts pieces (1, 2 or 4) of 128 / kPParts keys, so that the PV
+// product of the first pieces runs while the softmax group still exponentiates the later ones.
+constexpr int kPParts = B200K_FMHA_P_PARTS;
+static_assert(kPParts == 1 || kPParts == 2 || kPParts == 4, "P is handed over in 1, 2 or 4 pieces");  // of every 4 score pairs, how many exponentials run on the FMA pipe
 
 template <int D>
 struct FmhaSmem {
@@ -171,8 +172,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* s_full = bars + 10;   // [2]
   uint64_t* p_ready = bars + 12;  // [2]
   uint64_t* o_full = bars + 14;   // [2]
-  uint64_t* p_half = bars + 16;   // [2]  first 64 keys of P stored
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 18);
+  uint64_t* p_part = bars + 16;   // [3][2]  piece 0, 1, 2 of P stored (the last piece signals p_ready)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 22);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -221,7 +222,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_ready[i], 128);
-      mbar_init(&p_half[i], 128);
+      for (int part = 0; part < 3; ++part) mbar_init(&p_part[part * 2 + i], 128);
       mbar_init(&o_full[i], 1);
     }
     fence_mbar_init();
@@ -336,20 +337,21 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         bool k_next_ready = false;
         for (int i = 0; i < 2 && ok; ++i) {
           if (j >= nb[i]) continue;
-          if (kSplitP) {
-            if (!mbar_wait(&p_half[i], j & 1)) {
-              fail();
-              break;
-            }
+          constexpr int kStepsPerPart = kTile / 16 / kPParts;
+#pragma unroll
+          for (int part = 0; part + 1 < kPParts; ++part) {
+            if (ok && !mbar_wait(&p_part[part * 2 + i], j & 1)) fail();
+            if (!ok) break;
             tc_fence_after();
-            issue_pv(i, s, j == 0, 0, kTile / 32);
+            issue_pv(i, s, j == 0, part * kStepsPerPart, (part + 1) * kStepsPerPart);
           }
+          if (!ok) break;
           if (!mbar_wait(&p_ready[i], j & 1)) {
             fail();
             break;
           }
           tc_fence_after();
-          issue_pv(i, s, j == 0, kSplitP ? kTile / 32 : 0, kTile / 16);
+          issue_pv(i, s, j == 0, (kPParts - 1) * kStepsPerPart, kTile / 16);
           if (j == nb[i] - 1) umma_commit<1>(&o_full[i]);
           if (j + 1 < nb[i]) {
             const int s1 = (j + 1) & 1;
@@ -445,14 +447,15 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint64_t sc2 = f2pack(sc, sc), neg2 = f2pack(neg, neg);
         uint64_t sum_a = f2pack(0.f, 0.f), sum_b = f2pack(0.f, 0.f);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t pk[32];
+        for (int qt = 0; qt < 4; ++qt) {
+          // a quarter of the block: 32 keys -> 16 packed columns
+          uint32_t pk[16];
 #pragma unroll
-          for (int e = 0; e < 32; e += 4) {
+          for (int e = 0; e < 16; e += 4) {
             // 8 scores = 4 pairs per step; the last EMU pairs go to the FMA pipe, the rest to the MUFU
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
-              const int k = c * 64 + (e + g) * 2;
+              const int k = qt * 32 + (e + g) * 2;
               const uint64_t x2 = fma2(f2pack(__uint_as_float(s[k]), __uint_as_float(s[k + 1])), sc2, neg2);
               float p0, p1;
               if (g >= 4 - EMU) {
@@ -470,11 +473,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               pk[e + g] = pack16<BF16>(p0, p1);
             }
           }
-          tmem_st32(s_tmem + c * 32, pk);
-          if (kSplitP && c == 0) {
+          tmem_st16(s_tmem + qt * 16, pk);
+          // hand the finished piece to the MMA warp (the last piece goes through p_ready below)
+          if (qt < 3 && (qt + 1) % (4 / kPParts) == 0) {
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(&p_half[i]);
+            mbar_arrive(&p_part[((qt + 1) / (4 / kPParts) - 1) * 2 + i]);
           }
         }
         tmem_st_wait();
@@ -621,8 +625,8 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
   uint64_t* p_ready = bars + 14;   // [2]
   uint64_t* o_full = bars + 16;    // [2]  last PV of the item done
   uint64_t* o_free = bars + 18;    // [2]  epilogue has read O_i out of TMEM
-  uint64_t* p_half = bars + 20;    // [2]  first 64 keys of P stored
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 22);
+  uint64_t* p_part = bars + 20;    // [3][2]  piece 0, 1, 2 of P stored (the last piece signals p_ready)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 26);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -643,7 +647,7 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_ready[i], 128);
-      mbar_init(&p_half[i], 128);
+      for (int part = 0; part < 3; ++part) mbar_init(&p_part[part * 2 + i], 128);
       mbar_init(&o_full[i], 1);
       mbar_init(&o_free[i], 128);
     }
@@ -785,21 +789,22 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
               fail();
               break;
             }
-            if (kSplitP) {
-              if (!mbar_wait(&p_half[i], pn[i] & 1)) {
-                fail();
-                break;
-              }
+            constexpr int kStepsPerPart = kTile / 16 / kPParts;
+#pragma unroll
+            for (int part = 0; part + 1 < kPParts; ++part) {
+              if (ok && !mbar_wait(&p_part[part * 2 + i], pn[i] & 1)) fail();
+              if (!ok) break;
               tc_fence_after();
-              issue_pv(i, vc & 1, j == 0, 0, kTile / 32);
+              issue_pv(i, vc & 1, j == 0, part * kStepsPerPart, (part + 1) * kStepsPerPart);
             }
+            if (!ok) break;
             if (!mbar_wait(&p_ready[i], pn[i] & 1)) {
               fail();
               break;
             }
             ++pn[i];
             tc_fence_after();
-            issue_pv(i, vc & 1, j == 0, kSplitP ? kTile / 32 : 0, kTile / 16);
+            issue_pv(i, vc & 1, j == 0, (kPParts - 1) * kStepsPerPart, kTile / 16);
             if (j == it.nb[i] - 1) {
               umma_commit<1>(&o_full[i]);
               ++on[i];
@@ -911,13 +916,15 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         const uint64_t sc2 = f2pack(sc, sc), neg2 = f2pack(neg, neg);
         uint64_t sum_a = f2pack(0.f, 0.f), sum_b = f2pack(0.f, 0.f);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t pk[32];
+        for (int qt = 0; qt < 4; ++qt) {
+          // a quarter of the block: 32 keys -> 16 packed columns
+          uint32_t pk[16];
 #pragma unroll
-          for (int e = 0; e < 32; e += 4) {
+          for (int e = 0; e < 16; e += 4) {
+            // 8 scores = 4 pairs per step; the last EMU pairs go to the FMA pipe, the rest to the MUFU
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
-              const int k = c * 64 + (e + g) * 2;
+              const int k = qt * 32 + (e + g) * 2;
               const uint64_t x2 = fma2(f2pack(__uint_as_float(s[k]), __uint_as_float(s[k + 1])), sc2, neg2);
               float p0, p1;
               if (g >= 4 - EMU) {
@@ -935,11 +942,12 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
               pk[e + g] = pack16<BF16>(p0, p1);
             }
           }
-          tmem_st32(s_tmem + c * 32, pk);
-          if (kSplitP && c == 0) {
+          tmem_st16(s_tmem + qt * 16, pk);
+          // hand the finished piece to the MMA warp (the last piece goes through p_ready below)
+          if (qt < 3 && (qt + 1) % (4 / kPParts) == 0) {
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(&p_half[i]);
+            mbar_arrive(&p_part[((qt + 1) / (4 / kPParts) - 1) * 2 + i]);
           }
         }
         tmem_st_wait();
