@@ -155,6 +155,25 @@ int b200k_fmha_decode_splitkv(const void* Q_device, const void* K_device,
                               void* workspace_device, size_t workspace_bytes,
                               b200k_stream_t stream);
 
+/*
+ * The same decode attention over a PAGED key/value cache: K_pages, V_pages are
+ * [num_pages, Hkv, page_size, D] addressed by (page, head, row) element strides,
+ * page_size a multiple of 64; logical keys [n*page_size, (n+1)*page_size) of sequence b
+ * live in page block_table[b*max_blocks + n] (int32, device).  kv_lens is required.
+ * Workspace as b200k_fmha_decode_workspace_bytes(B, Hq, Hkv, Sq, max_blocks*page_size, D,
+ * num_splits).  The TMA producer looks the page up per 64-key tile; nothing else differs
+ * from b200k_fmha_decode_splitkv, and for the same cache contents and split count the
+ * results are bit-identical.  No counterpart in the reference (its KV tensors are dense).
+ */
+int b200k_fmha_decode_paged(const void* Q_device, const void* K_pages_device, const void* V_pages_device,
+                            void* O_device, int B, int Hq, int Hkv, int Sq, int D,
+                            int num_pages, int page_size,
+                            const int64_t q_strides[3], const int64_t k_page_strides[3],
+                            const int64_t v_page_strides[3], const int64_t o_strides[3],
+                            float scale, const int32_t* block_table_device, int max_blocks,
+                            const int32_t* kv_lens_device, int num_splits, int dtype,
+                            void* workspace_device, size_t workspace_bytes, b200k_stream_t stream);
+
 size_t b200k_fmha_decode_workspace_bytes(int B, int Hq, int Hkv, int Sq, int Skv, int D,
                                          int num_splits);
 

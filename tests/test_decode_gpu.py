@@ -116,3 +116,33 @@ def test_workspace_errors(cuda_device):
     assert e.value.code == -5
     with pytest.raises(_lib.B200KError):  # 32 rows per KV head do not fit the 16-row tile
         fmha.fmha_decode(*inputs.fmha_inputs(1, 32, 1, 1, 128, 128, torch.float16, device=cuda_device))
+
+
+@pytest.mark.parametrize("page_size", [64, 128, 256])
+def test_paged_cache_matches_dense(cuda_device, page_size):
+    """A paged cache holding the same keys/values as a dense one (pages scattered by a random
+    permutation, unused table entries pointing nowhere) gives bit-identical results."""
+    from b200k import fmha, inputs
+    B, Hq, Hkv, Skv, D = 5, 32, 8, 2048, 128
+    q, k, v = inputs.fmha_inputs(B, Hq, Hkv, 1, Skv, D, torch.float16, device=cuda_device, seed=61)
+    lens = torch.tensor([2048, 1, 700, 65, 1999], dtype=torch.int32, device=cuda_device)
+    blocks = Skv // page_size
+    g = torch.Generator().manual_seed(3)
+    perm = torch.randperm(B * blocks + 7, generator=g)[:B * blocks].to(torch.int32)  # 7 spare pages
+    table = perm.view(B, blocks).to(cuda_device)
+    num_pages = B * blocks + 7
+    k_pages = torch.full((num_pages, Hkv, page_size, D), float("nan"), dtype=torch.float16, device=cuda_device)
+    v_pages = torch.full_like(k_pages, float("nan"))
+    for b in range(B):
+        for n in range(blocks):
+            k_pages[table[b, n]] = k[b, :, n * page_size:(n + 1) * page_size]
+            v_pages[table[b, n]] = v[b, :, n * page_size:(n + 1) * page_size]
+    # blocks entirely beyond a sequence's length are never looked at: poison their table entries
+    poisoned = table.clone()
+    for b in range(B):
+        first_unused = (int(lens[b]) + page_size - 1) // page_size
+        poisoned[b, first_unused:] = -12345
+    dense = fmha.fmha_decode(q, k, v, kv_lens=lens, num_splits=4)
+    paged = fmha.fmha_decode_paged(q, k_pages, v_pages, poisoned, lens, num_splits=4)
+    assert torch.equal(paged, dense)
+    assert oracle.max_abs(paged, oracle.fmha_ref(q, k, v, kv_lens=lens)) <= TOL

@@ -37,6 +37,9 @@ SIGNATURES = {
                                                  c_int, c_int, _I64x3, _I64x3, _I64x3, _I64x3, c_float, c_void_p,
                                                  c_int, c_int, c_void_p]),
     "b200k_fmha_decode_static_scratch_bytes": (c_size_t, []),
+    "b200k_fmha_decode_paged": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                        c_int, _I64x3, _I64x3, _I64x3, _I64x3, c_float, c_void_p, c_int, c_void_p,
+                                        c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "b200k_fmha_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
     "b200k_fmha_decode_auto_splits": (c_int, [c_int, c_int, c_int]),
     "b200k_strerror": (c_char_p, [c_int]),

@@ -102,3 +102,39 @@ def fmha_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_lens: torc
             workspace.data_ptr(), workspace.numel(), torch.cuda.current_stream(q.device).cuda_stream)
     _lib.check(code, "b200k_fmha_decode_splitkv")
     return out
+
+
+def fmha_decode_paged(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                      kv_lens: torch.Tensor, num_splits: int = 0, scale: float | None = None,
+                      out: torch.Tensor | None = None) -> torch.Tensor:
+    """Decode attention over a paged cache: k_pages, v_pages [num_pages, Hkv, page_size, D] (page_size a
+    multiple of 64), block_table int32 [B, max_blocks] (page of every logical block), kv_lens int32 [B]."""
+    if q.dim() != 4 or k_pages.dim() != 4 or k_pages.shape != v_pages.shape:
+        raise RuntimeError("q must be [B,Hq,Sq,D]; k_pages and v_pages [num_pages,Hkv,page_size,D]")
+    if q.dtype not in _DTYPES or k_pages.dtype != q.dtype or v_pages.dtype != q.dtype:
+        raise RuntimeError("q, k_pages, v_pages must all be float16 or bfloat16")
+    B, Hq, Sq, D = q.shape
+    num_pages, Hkv, page_size, Dk = k_pages.shape
+    if Dk != D or block_table.dim() != 2 or block_table.size(0) != B or block_table.dtype != torch.int32:
+        raise RuntimeError("block_table must be int32 [B, max_blocks] and head_dim must match")
+    if kv_lens.dtype != torch.int32 or kv_lens.numel() != B:
+        raise RuntimeError("kv_lens must be int32 [B]")
+    if not all(t.is_cuda and t.device == q.device for t in (k_pages, v_pages, block_table, kv_lens)):
+        raise RuntimeError("all tensors must be on q's CUDA device")
+    q, k_pages, v_pages = _rows_contiguous(q), _rows_contiguous(k_pages), _rows_contiguous(v_pages)
+    block_table, kv_lens = block_table.contiguous(), kv_lens.contiguous()
+    max_blocks = block_table.size(1)
+    if out is None:
+        out = torch.empty((B, Hq, Sq, D), dtype=q.dtype, device=q.device)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    L = _lib.lib()
+    with torch.cuda.device(q.device):
+        ws = decode_workspace(B, Hq, Hkv, Sq, max_blocks * page_size, D, num_splits, q.device)
+        code = L.b200k_fmha_decode_paged(
+            q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), B, Hq, Hkv, Sq, D, num_pages,
+            page_size, _lib.strides3(q), _lib.strides3(k_pages), _lib.strides3(v_pages), _lib.strides3(out),
+            float(scale), block_table.data_ptr(), max_blocks, kv_lens.data_ptr(), int(num_splits), _DTYPES[q.dtype],
+            ws.data_ptr(), ws.numel(), torch.cuda.current_stream(q.device).cuda_stream)
+    _lib.check(code, "b200k_fmha_decode_paged")
+    return out

@@ -59,6 +59,12 @@ struct DecParams {
   int chunk;       // keys per split (multiple of kDecTile)
   float scale_log2;
   int* status;
+  // paged K/V (block_table == nullptr: one contiguous [B,Hkv,Skv,D] tensor each): the tensor maps
+  // then cover [num_pages, Hkv, page_size, D] and logical keys [n*page_size, (n+1)*page_size) of
+  // sequence b live in page block_table[b*max_blocks + n]; page_size is a multiple of the 64-key tile
+  const int32_t* block_table;
+  int max_blocks;
+  int page_size;
 };
 
 __device__ __forceinline__ float ex2f(float x) {
@@ -158,11 +164,19 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         uint8_t* sk = smem + stage * L::kStageBytes;
         uint8_t* sv = sk + L::kTileBytes;
         mbar_expect_tx(&full_bar[stage], L::kStageBytes);
-        const int key0 = k_begin + t * kDecTile;
+        int key0 = k_begin + t * kDecTile;
+        int outer = b;
+        if (p.block_table) {
+          // a 64-key tile never straddles pages; an out-of-range page index makes TMA read zeros
+          outer = p.block_table[(int64_t)b * p.max_blocks + key0 / p.page_size];
+          key0 %= p.page_size;
+        }
 #pragma unroll
-        for (int d = 0; d < kDBoxes; ++d) tma_load_4d(sk + d * L::kHalfBytes, &tmK, &full_bar[stage], d * 64, key0, hk, b);
+        for (int d = 0; d < kDBoxes; ++d)
+          tma_load_4d(sk + d * L::kHalfBytes, &tmK, &full_bar[stage], d * 64, key0, hk, outer);
 #pragma unroll
-        for (int d = 0; d < kDBoxes; ++d) tma_load_4d(sv + d * L::kHalfBytes, &tmV, &full_bar[stage], d * 64, key0, hk, b);
+        for (int d = 0; d < kDBoxes; ++d)
+          tma_load_4d(sv + d * L::kHalfBytes, &tmV, &full_bar[stage], d * 64, key0, hk, outer);
         if (++stage == kDecStages) {
           stage = 0;
           phase ^= 1;
@@ -404,7 +418,8 @@ int chunk_of(int Skv, int splits) {
 template <int D, bool BF16>
 int launch_decode(const void* Q, const void* K, const void* V, void* O, int B, int Hq, int Hkv, int Sq, int Skv,
                   const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, float scale,
-                  const int32_t* kv_lens, int splits, float* part_o, float* part_ml, cudaStream_t stream) {
+                  const int32_t* kv_lens, int splits, float* part_o, float* part_ml, cudaStream_t stream,
+                  const int32_t* block_table = nullptr, int max_blocks = 0, int page_size = 0, int num_pages = 0) {
   using L = DecSmem<D>;
   auto kfn = decode_splitkv_kernel<D, BF16>;
   static bool configured[64] = {};
@@ -419,7 +434,9 @@ int launch_decode(const void* Q, const void* K, const void* V, void* O, int B, i
   }
   CUtensorMap tmK, tmV;
   {
-    uint64_t dims[4] = {(uint64_t)D, (uint64_t)Skv, (uint64_t)Hkv, (uint64_t)B};
+    // contiguous: (D, Skv, Hkv, B); paged: (D, page_size, Hkv, num_pages) with Skv = max_blocks * page_size
+    uint64_t dims[4] = {(uint64_t)D, (uint64_t)(block_table ? page_size : Skv), (uint64_t)Hkv,
+                        (uint64_t)(block_table ? num_pages : B)};
     uint32_t box[4] = {64, (uint32_t)kDecTile, 1, 1};
     uint64_t kstr[3] = {(uint64_t)ks[2] * 2, (uint64_t)ks[1] * 2, (uint64_t)ks[0] * 2};
     uint64_t vstr[3] = {(uint64_t)vs[2] * 2, (uint64_t)vs[1] * 2, (uint64_t)vs[0] * 2};
@@ -444,6 +461,9 @@ int launch_decode(const void* Q, const void* K, const void* V, void* O, int B, i
   p.num_splits = splits;
   p.chunk = chunk_of(Skv, splits);
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.block_table = block_table;
+  p.max_blocks = max_blocks;
+  p.page_size = page_size;
   p.status = status_ptr();
   if (!p.status) return B200K_ECUDA;
   dim3 grid(splits, Hkv, B);
@@ -504,6 +524,49 @@ extern "C" int b200k_fmha_decode_splitkv(const void* Q, const void* K, const voi
 #define B200K_DECODE(DD, BF)                                                                                     \
   launch_decode<DD, BF>(Q, K, V, O, B, Hq, Hkv, Sq, Skv, q_strides, k_strides, v_strides, o_strides, scale, kv_lens, \
                         splits, part_o, part_ml, stream)
+  if (D == 128) return bf16 ? B200K_DECODE(128, true) : B200K_DECODE(128, false);
+  return bf16 ? B200K_DECODE(64, true) : B200K_DECODE(64, false);
+#undef B200K_DECODE
+}
+
+extern "C" int b200k_fmha_decode_paged(const void* Q, const void* K_pages, const void* V_pages, void* O, int B, int Hq,
+                                       int Hkv, int Sq, int D, int num_pages, int page_size,
+                                       const int64_t q_strides[3], const int64_t k_page_strides[3],
+                                       const int64_t v_page_strides[3], const int64_t o_strides[3], float scale,
+                                       const int32_t* block_table, int max_blocks, const int32_t* kv_lens,
+                                       int num_splits, int dtype, void* workspace, size_t workspace_bytes,
+                                       b200k_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (dtype != B200K_F16 && dtype != B200K_BF16) return B200K_EDTYPE;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Hq % Hkv != 0 || num_pages <= 0 || max_blocks <= 0)
+    return B200K_ESHAPE;
+  if (page_size <= 0 || page_size % kDecTile != 0) return B200K_ESHAPE;
+  if ((long)max_blocks * page_size > 0x7fffffffL) return B200K_ESHAPE;
+  if (D != 64 && D != 128) return B200K_EHEADDIM;
+  if (Hq / Hkv * Sq > kMaxRows) return B200K_ESHAPE;
+  if (!Q || !K_pages || !V_pages || !O || !block_table || !kv_lens || !q_strides || !k_page_strides ||
+      !v_page_strides || !o_strides)
+    return B200K_EARG;
+  if (!(scale > 0.f) || num_splits < 0 || num_splits > 1024) return B200K_EARG;
+  auto ok16 = [](const void* ptr, const int64_t* st) {
+    return aligned16(ptr) && st[0] % 8 == 0 && st[1] % 8 == 0 && st[2] % 8 == 0;
+  };
+  if (!ok16(K_pages, k_page_strides) || !ok16(V_pages, v_page_strides)) return B200K_EALIGN;
+  if ((reinterpret_cast<uintptr_t>(Q) & 3) || q_strides[0] % 2 || q_strides[1] % 2 || q_strides[2] % 2)
+    return B200K_EALIGN;
+  if (!b200k_device_supported()) return B200K_ENOGPU;
+  const int Skv = max_blocks * page_size;  // logical capacity of a sequence
+  const int splits = num_splits > 0 ? num_splits : choose_splits(B, Hkv, Skv);
+  const size_t need = b200k_fmha_decode_workspace_bytes(B, Hq, Hkv, Sq, Skv, D, splits);
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15)) return B200K_EWORKSPACE;
+  const size_t rows = (size_t)B * Hkv * (size_t)(Hq / Hkv * Sq);
+  float* part_o = reinterpret_cast<float*>(workspace);
+  float* part_ml = part_o + rows * splits * D;
+  const bool bf16 = dtype == B200K_BF16;
+#define B200K_DECODE(DD, BF)                                                                                    \
+  launch_decode<DD, BF>(Q, K_pages, V_pages, O, B, Hq, Hkv, Sq, Skv, q_strides, k_page_strides, v_page_strides,  \
+                        o_strides, scale, kv_lens, splits, part_o, part_ml, stream, block_table, max_blocks,     \
+                        page_size, num_pages)
   if (D == 128) return bf16 ? B200K_DECODE(128, true) : B200K_DECODE(128, false);
   return bf16 ? B200K_DECODE(64, true) : B200K_DECODE(64, false);
 #undef B200K_DECODE
