@@ -310,21 +310,65 @@ def run_ours(args):
     a_h = a.cpu().pin_memory()
     w_h = w.cpu().pin_memory()
     c_h = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
-    a_d = torch.empty_like(a)
-    w_d = torch.empty_like(w)
+    # Pipelined over three buffer sets: step s copies its operands in on one stream while step s-1 computes on a
+    # second and step s-2's result is read back on a third, so the PCIe directions and the GPU
+    # overlap; every step still moves all of its inputs and its whole result.
+    nbuf = 3
+    a_d = [torch.empty_like(a) for _ in range(nbuf)]
+    w_d = [torch.empty_like(w) for _ in range(nbuf)]
+    c_hs = [c_h] + [torch.empty((M, N), dtype=torch.bfloat16).pin_memory() for _ in range(nbuf - 1)]
+    st_in, st_run, st_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
 
-    def e2e_step():
-        a_d.copy_(a_h, non_blocking=True)
-        w_d.copy_(w_h, non_blocking=True)
-        out = gemm_unified.ops.fine_gemm(a_d, w_d, 12)
-        c_h.copy_(out, non_blocking=True)
+    def e2e_run(nsteps):
+        main = torch.cuda.current_stream()
+        start = torch.cuda.Event(enable_timing=True)
+        stop = torch.cuda.Event(enable_timing=True)
+        start.record(main)
+        for st in (st_in, st_run, st_out):
+            st.wait_event(start)
+        ran = [None] * nbuf      # compute finished with buffer set i
+        read = [None] * nbuf     # result of buffer set i is back on the host
+        keep = [None] * nbuf
+        for step_i in range(nsteps):
+            i = step_i % nbuf
+            with torch.cuda.stream(st_in):
+                if ran[i] is not None:
+                    st_in.wait_event(ran[i])          # operands of set i no longer in use
+                a_d[i].copy_(a_h, non_blocking=True)
+                w_d[i].copy_(w_h, non_blocking=True)
+                loaded = torch.cuda.Event()
+                loaded.record(st_in)
+            with torch.cuda.stream(st_run):
+                st_run.wait_event(loaded)
+                out = gemm_unified.ops.fine_gemm(a_d[i], w_d[i], 12)
+                ran[i] = torch.cuda.Event()
+                ran[i].record(st_run)
+            with torch.cuda.stream(st_out):
+                st_out.wait_event(ran[i])
+                if read[i] is not None:
+                    st_out.wait_event(read[i])
+                out.record_stream(st_out)
+                c_hs[i].copy_(out, non_blocking=True)
+                read[i] = torch.cuda.Event()
+                read[i].record(st_out)
+            keep[i] = out
+        for st in (st_in, st_run, st_out):
+            done = torch.cuda.Event()
+            done.record(st)
+            main.wait_event(done)
+        stop.record(main)
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / 1e3
 
-    e2e_steps = max(3, min(steps, 10))
-    e2e_secs = max_over_ranks(time_cuda(e2e_step, e2e_steps, 3, barrier))
+    e2e_steps = max(4, min(steps, 12))
+    e2e_run(4)  # warm-up
+    barrier()
+    e2e_secs = max_over_ranks(e2e_run(e2e_steps))
+    barrier()
     e2e_value = world * FLOPS_PER_STEP * e2e_steps / e2e_secs / 1e12
     h2d = a_h.numel() * 2 + w_h.numel() * 2
     d2h = c_h.numel() * 2
-    del a_h, w_h, c_h, a_d, w_d
+    del a_h, w_h, c_h, c_hs, a_d, w_d
 
     # ---- extra: FMHA prefill (causal, s=4096) and split-KV decode ----
     extra = {}
@@ -429,7 +473,7 @@ def run_ours(args):
                          "algorithmic": algorithmic, "frac_of_nominal_2250": kernel_tflops / 2250.0},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "api": "gemm_unified.ops.fine_gemm(a, b, 12)"},
+                    "api": "gemm_unified.ops.fine_gemm(a, b, 12)", "pipelining": "3 buffer sets, copy-in / compute / copy-out streams"},
             "gpu_launches": int(launches),
             "clocks": clocks,
             "extra": extra,
