@@ -19,8 +19,11 @@
 // the row sum.  The MUFU delivers only 16 exponentials per clock per SM, which makes one
 // softmax pass about as long as the two MMAs of a tile; a quarter of the exponentials
 // therefore runs as a polynomial on the FMA pipe (measured +3 %; a half costs more issue
-// slots than it frees MUFU cycles).  The epilogue scales O by 1/l, stages it in the (now free) Q tile
-// and stores it with TMA, which also clips the ragged last tile.
+// slots than it frees MUFU cycles).  P reaches the MMA warp in two halves of 64 keys, so the first
+// half of the PV product overlaps the second half of the exponentials.  The epilogue scales O by 1/l,
+// stages it in the (now free) Q tile and stores it with TMA, which also clips the ragged last tile.
+// Two kernels share this design: one work item per CTA (fmha_fwd_kernel, default for kv_len > 4096)
+// and a persistent one (fmha_fwd_persistent_kernel, further down, default up to 4096).
 //
 // Reference semantics: kernels/fmha/pkg/fmha_unified/csrc/semi/fmha_2_nv.cu
 // (:36-48 GQA + offsets, :93-97 causal block range, :177-185 mask + scale,
