@@ -429,6 +429,53 @@ def run_ours(args):
     except Exception as exc:  # the headline number stands even if an extra fails
         extra["error"] = repr(exc)[:300]
 
+    # ---- strong scaling of the attention paths: a FIXED problem sharded over the ranks ----
+    # prefill: bf16, B=8, 32 heads (MHA), s=2048, d=128, causal, (batch, head) pairs dealt to the ranks;
+    # decode: the 64-sequence batch above, sequences balanced by total KV length.  No collective: the
+    # output stays sharded; the time is the slowest rank's.
+    try:
+        from b200k import shard as _shard
+        Bp, Hp, Sp, Dp = 8, 32, 2048, 128
+        mine = _shard.head_shards(Bp, Hp, Hp, world)[rank]
+        parts = []
+        for (bb, h0, nh) in mine:
+            qs = inputs.device_randn16((1, nh, Sp, Dp), 300 + bb * Hp + h0, 1.0, torch.bfloat16, dev)
+            parts.append((qs, torch.randn_like(qs), torch.randn_like(qs), torch.empty_like(qs)))
+
+        def prefill_shard():
+            for (q_, k_, v_, o_) in parts:
+                fmha.fmha_fwd(q_, k_, v_, causal=True, out=o_)
+
+        psteps = max(steps, 10)
+        psecs = max_over_ranks(time_cuda(prefill_shard, psteps, warmup, barrier))
+        pflops = 4.0 * Bp * Hp * Sp * Sp * Dp * 0.5
+        extra["fmha_prefill_sharded"] = {
+            "workload": "causal_fmha_bf16_B8_H32_S2048_D128 over all ranks ((batch, head) shards)",
+            "value": pflops * psteps / psecs / 1e12, "unit": "TFLOP/s", "ms": psecs / psteps * 1e3,
+            "scaling": "strong", "launches_per_rank": len(parts)}
+        del parts
+        Bd, Hqd, Hkvd, Skvd, Dd = 64, 32, 8, 32768, 128
+        all_lens = inputs.decode_lens(Bd)
+        idx = _shard.balance_sequences(all_lens.tolist(), world)[rank]
+        nb_ = len(idx)
+        lens_r = all_lens[idx].to(dev)
+        qd = inputs.device_randn16((nb_, Hqd, 1, Dd), 7, 1.0, torch.float16, dev)
+        kd = inputs.device_randn16((nb_, Hkvd, Skvd, Dd), 8, 1.0, torch.float16, dev)
+        vd = inputs.device_randn16((nb_, Hkvd, Skvd, Dd), 9, 1.0, torch.float16, dev)
+        od = torch.empty_like(qd)
+        wsd = fmha.decode_workspace(nb_, Hqd, Hkvd, 1, Skvd, Dd, 0, dev)
+        dsteps2 = max(steps, 10)
+        dsecs2 = max_over_ranks(time_cuda(
+            lambda: fmha.fmha_decode(qd, kd, vd, kv_lens=lens_r, out=od, workspace=wsd), dsteps2, warmup, barrier))
+        dbytes2 = float(all_lens.sum().item()) * Hkvd * Dd * 4 + 2.0 * Bd * Hqd * Dd * 2
+        extra["decode_sharded"] = {
+            "workload": "the 64-sequence decode batch over all ranks (sequences balanced by KV length)",
+            "value": dbytes2 * dsteps2 / dsecs2 / 1e9, "unit": "GB/s", "ms": dsecs2 / dsteps2 * 1e3,
+            "scaling": "strong", "sequences_this_rank": nb_}
+        del qd, kd, vd, od, wsd
+    except Exception as exc:
+        extra["sharded_error"] = repr(exc)[:300]
+
     # ---- N > 1: the one collective of the GEMM path, reassembling a column-sharded product ----
     if distributed:
         try:
