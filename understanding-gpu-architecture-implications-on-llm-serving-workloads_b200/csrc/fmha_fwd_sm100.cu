@@ -555,6 +555,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // of the current one.  The epilogue stages O in its own 16 KB buffer per warpgroup (64 columns at a
 // time) instead of the Q tile, which the loader may already be refilling.
 // ---------------------------------------------------------------------------------------------
+// Register split of the persistent kernel (per thread; 256 softmax threads + 128 others must fit the
+// 64K registers of the SM): its loader and MMA threads carry more running state than in the one-item kernel.
+constexpr int kPersistAuxRegs = 88, kPersistSoftmaxRegs = 208;
+
 template <int D>
 struct FmhaPSmem {
   static constexpr uint32_t kTileBytes = kTile * D * 2;
@@ -670,10 +674,10 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp >= 10) {
-    reg_dealloc<56>();
+    reg_dealloc<kPersistAuxRegs>();
   } else if (warp == 8) {
     // ------------------------------- TMA loader -------------------------------
-    reg_dealloc<56>();
+    reg_dealloc<kPersistAuxRegs>();
     if (elect_one()) {
       uint32_t kc = 0, vc = 0, qn[2] = {0, 0};
       bool ok = true;
@@ -723,7 +727,7 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     }
   } else if (warp == 9) {
     // ------------------------------- MMA issuer -------------------------------
-    reg_dealloc<56>();
+    reg_dealloc<kPersistAuxRegs>();
     if (elect_one()) {
       constexpr uint32_t idesc_s = make_idesc_f16(BF16 ? 1 : 0, 0, 0, kTile, kTile);
       constexpr uint32_t idesc_pv = make_idesc_f16(BF16 ? 1 : 0, 0, 1, kTile, D);
@@ -838,7 +842,7 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     }
   } else {
     // ----------------------------- softmax groups -----------------------------
-    reg_alloc<224>();
+    reg_alloc<kPersistSoftmaxRegs>();
     const int i = warp >> 2;
     const int row = threadIdx.x & 127;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
@@ -965,8 +969,8 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       if (!ok) break;
 
       // ------------------------------ epilogue ------------------------------
-      uint32_t o[D];
-      if (it.nb[i] > 0) {
+      const bool have_o = it.nb[i] > 0;
+      if (have_o) {
         if (!mbar_wait(&o_full[i], itn & 1)) {
           if (lane == 0) report_timeout(p.status, KID_FMHA, ROLE_EPILOGUE);
           ok = false;
@@ -974,18 +978,24 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         }
         ++itn;
         tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) tmem_ld32(o_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&o[c * 32]));
-        tmem_ld_wait();
-        tc_fence_before();
-        mbar_arrive(&o_free[i]);  // the next item's first PV may overwrite O_i now
-      } else {
-#pragma unroll
-        for (int e = 0; e < D; ++e) o[e] = 0u;
       }
       const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
       for (int hb = 0; hb < kDBoxes; ++hb) {
+        // 64 columns of O at a time: TMEM -> registers -> staging buffer -> TMA store
+        uint32_t o[64];
+        if (have_o) {
+          tmem_ld32(o_tmem + hb * 64, *reinterpret_cast<uint32_t(*)[32]>(&o[0]));
+          tmem_ld32(o_tmem + hb * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&o[32]));
+          tmem_ld_wait();
+          if (hb == kDBoxes - 1) {
+            tc_fence_before();
+            mbar_arrive(&o_free[i]);  // all of O_i is in registers: the next item's first PV may overwrite it
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 64; ++e) o[e] = 0u;
+        }
         // the previous TMA store out of this staging buffer must have finished reading it
         if (store_pending) {
           if (row == 0) tma_store_wait_read<0>();
@@ -994,7 +1004,7 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         uint8_t* rowp = stage + row * 128;
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
-          const int e = hb * 64 + g * 8;
+          const int e = g * 8;
           uint4 wv;
           wv.x = pack16<BF16>(__uint_as_float(o[e + 0]) * inv, __uint_as_float(o[e + 1]) * inv);
           wv.y = pack16<BF16>(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
