@@ -129,11 +129,28 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(inside), "source": "nvml polling during the timed region"}
 
 
-def time_cuda(fn, steps: int, warmup: int, barrier=None, sampler=None) -> float:
+def warm_for(fn, seconds: float) -> None:
+    """Calls fn until about `seconds` of device time have passed: after host-side set-up (input
+    generation, copies) the GPU has dropped to idle clocks, and a sub-millisecond kernel timed right
+    after a handful of warm-up calls is measured on the ramp, not at the clocks it runs at in a job."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    total = 0.0
+    while total < seconds:
+        e0.record()
+        for _ in range(8):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1) / 1e3
+
+
+def time_cuda(fn, steps: int, warmup: int, barrier=None, sampler=None, warm_seconds: float = 0.0) -> float:
     """Seconds for `steps` calls of fn, CUDA events on the current stream, after warm-up."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    if warm_seconds > 0:
+        warm_for(fn, warm_seconds)
     if barrier:
         barrier()
     torch.cuda.synchronize()
@@ -375,8 +392,9 @@ def run_ours(args):
     try:
         q, k, v = inputs.fmha_c3(dev)
         o = torch.empty_like(q)
-        fsteps = max(steps, 10)
-        fsecs = max_over_ranks(time_cuda(lambda: fmha.fmha_fwd(q, k, v, causal=True, out=o), fsteps, warmup, barrier))
+        fsteps = max(steps, 50)
+        fsecs = max_over_ranks(time_cuda(lambda: fmha.fmha_fwd(q, k, v, causal=True, out=o), fsteps, warmup, barrier,
+                                         warm_seconds=0.03))
         fflops = 4.0 * 1 * 32 * 4096 * 4096 * 128 * 0.5
         tf = world * fflops * fsteps / fsecs / 1e12
         extra["fmha_prefill"] = {
@@ -395,7 +413,8 @@ def run_ours(args):
         ws = fmha.decode_workspace(B, Hq, Hkv, 1, Skv, D, 0, dev)
         dsteps = max(steps, 10)
         dsecs = max_over_ranks(time_cuda(
-            lambda: fmha.fmha_decode(qd, kd, vd, kv_lens=lens, out=od, workspace=ws), dsteps, warmup, barrier))
+            lambda: fmha.fmha_decode(qd, kd, vd, kv_lens=lens, out=od, workspace=ws), dsteps, warmup, barrier,
+            warm_seconds=0.03))
         dbytes = float(lens.sum().item()) * Hkv * D * 2 * 2 + 2.0 * B * Hq * D * 2
         gbs = world * dbytes * dsteps / dsecs / 1e9
         extra["decode_splitkv"] = {
@@ -416,8 +435,8 @@ def run_ours(args):
             turn[0] = (turn[0] + 1) % len(wts)
             gemm.gemm(xs, wts[turn[0]], out=cs)
 
-        ssteps = max(steps, 40)
-        ssecs = max_over_ranks(time_cuda(skinny_step, ssteps, warmup, barrier))
+        ssteps = max(steps, 200)
+        ssecs = max_over_ranks(time_cuda(skinny_step, ssteps, warmup, barrier, warm_seconds=0.03))
         sbytes = 2.0 * (Ks * Ns + Ms * Ks + Ms * Ns)
         sgbs = world * sbytes * ssteps / ssecs / 1e9
         extra["skinny_gemm"] = {

@@ -4,7 +4,8 @@
 
 The counterpart of the reference's perf sweeps (kernels/gemm/test/perf.py:62-77,
 kernels/fmha/test/perf.py:100-113), which print a TFLOPS table per kernel index; here every
-case is timed with CUDA events (3 warm-ups, >= 10 launches; weights of memory-bound GEMMs are
+case is timed with CUDA events (about 30 ms of warm-up so the clocks have ramped, then the median of
+5 repeats of >= 10 launches, alternating with the comparator; weights of memory-bound GEMMs are
 rotated through 8 copies so they stream from HBM), next to the library comparators the
 reference also uses as its kernels -1 / -2 (torch.matmul, scaled_dot_product_attention).
 Rates: TFLOP/s = 2MNK/t (GEMM), 4*B*H*Sq*Skv*D/t, halved when causal (FMHA; the reference's
@@ -14,6 +15,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import statistics
 import sys
 
 import torch
@@ -22,10 +24,21 @@ import torch.nn.functional as F
 from . import fmha, gemm, inputs
 
 
-def _time(fn, n):
-    for _ in range(3):
-        fn()
-    torch.cuda.synchronize()
+def _warm(fn, seconds=0.03):
+    """Runs fn for about `seconds` of device time: after input generation the GPU sits at idle clocks,
+    and a short kernel timed after a few calls only would be measured on the clock ramp."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    total = 0.0
+    while total < seconds:
+        e0.record()
+        for _ in range(8):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1) / 1e3
+
+
+def _time_once(fn, n):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(n):
@@ -33,6 +46,23 @@ def _time(fn, n):
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / n / 1e3
+
+
+def _time_pair(fn_a, fn_b, n, repeats=5):
+    """Median seconds per call of two candidates, timed in alternation (a, b, a, b, ...) after both
+    have warmed up, so that neither is favoured by the clocks the other left behind."""
+    _warm(fn_a)
+    _warm(fn_b)
+    ta, tb = [], []
+    for _ in range(repeats):
+        ta.append(_time_once(fn_a, n))
+        tb.append(_time_once(fn_b, n))
+    return statistics.median(ta), statistics.median(tb)
+
+
+def _time(fn, n, repeats=5):
+    _warm(fn)
+    return statistics.median(_time_once(fn, n) for _ in range(repeats))
 
 
 def gemm_case(M, K, N, dtype, dev, n=20):
@@ -51,7 +81,7 @@ def gemm_case(M, K, N, dtype, dev, n=20):
         torch.matmul(a, ws[turn[0]], out=out)
 
     n = n if M > 128 else 4 * n
-    t, t_lib = _time(ours, n), _time(lib, n)
+    t, t_lib = _time_pair(ours, lib, n)
     flops, nbytes = 2.0 * M * N * K, 2.0 * (M * K + K * N + M * N)
     return {"path": "gemm", "M": M, "K": K, "N": N, "dtype": str(dtype).split(".")[-1], "us": t * 1e6,
             "tflops": flops / t / 1e12, "gbs": nbytes / t / 1e9, "cublas_tflops": flops / t_lib / 1e12,
@@ -63,8 +93,8 @@ def fmha_case(B, Hq, Hkv, S, D, causal, dtype, dev, n=10):
     k = inputs.device_randn16((B, Hkv, S, D), 2, 1.0, dtype, dev)
     v = inputs.device_randn16((B, Hkv, S, D), 3, 1.0, dtype, dev)
     out = torch.empty_like(q)
-    t = _time(lambda: fmha.fmha_fwd(q, k, v, causal=causal, out=out), n)
-    t_lib = _time(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=causal, enable_gqa=True), n)
+    t, t_lib = _time_pair(lambda: fmha.fmha_fwd(q, k, v, causal=causal, out=out),
+                          lambda: F.scaled_dot_product_attention(q, k, v, is_causal=causal, enable_gqa=True), n)
     flops = 4.0 * B * Hq * S * S * D * (0.5 if causal else 1.0)
     return {"path": "fmha", "B": B, "Hq": Hq, "Hkv": Hkv, "S": S, "D": D, "causal": causal,
             "dtype": str(dtype).split(".")[-1], "us": t * 1e6, "tflops": flops / t / 1e12,

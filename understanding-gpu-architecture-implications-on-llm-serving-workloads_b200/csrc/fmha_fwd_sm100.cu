@@ -153,6 +153,119 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
   }
 }
 
+// One 128-key block of the online softmax for one query row (one thread): S row from TMEM ->
+// P = 2^(S*scale - m) as 16-bit pairs over the same TMEM columns, handed to the MMA warp in kPParts
+// pieces; l and m are the running row sum and the maximum in use.  Rescaling is lazy: m moves (and
+// O and l are scaled) only when the new maximum exceeds it by more than kRescaleThreshold in some
+// row of the warp, so P may reach 2^threshold.
+//   lim: local index of the last visible key of this row in this block (masked = some row of the tile
+//   has lim < 127); s_tmem / o_tmem: this thread's lane of the S and O accumulators.
+template <int D, bool BF16, int EMU>
+__device__ __forceinline__ void softmax_block(uint32_t s_tmem, uint32_t o_tmem, bool first, bool masked, int lim,
+                                              float sc, float& m_use, float& l, uint64_t* p_part_i,
+                                              uint64_t* p_ready_i) {
+  uint32_t s[128];
+  tmem_ld32(s_tmem + 0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+  tmem_ld32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+  tmem_ld32(s_tmem + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
+  tmem_ld32(s_tmem + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
+  tmem_ld_wait();
+  if (masked) {
+#pragma unroll
+    for (int k = 0; k < 128; ++k)
+      if (k > lim) s[k] = 0xff800000u;  // -inf
+  }
+  auto row_max = [&]() {
+    float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < 128; k += 8) {
+      mx0 = max3(mx0, __uint_as_float(s[k + 0]), __uint_as_float(s[k + 1]));
+      mx1 = max3(mx1, __uint_as_float(s[k + 2]), __uint_as_float(s[k + 3]));
+      mx2 = max3(mx2, __uint_as_float(s[k + 4]), __uint_as_float(s[k + 5]));
+      mx3 = max3(mx3, __uint_as_float(s[k + 6]), __uint_as_float(s[k + 7]));
+    }
+    return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc;
+  };
+  // moves m to m_new: l and the O accumulator (the PV products of the earlier blocks are complete:
+  // this block's S was issued behind them) are scaled by 2^(m - m_new)
+  auto rescale_to = [&](float m_new) {
+    const float f = (m_new == -INFINITY) ? 1.f : ex2(m_use - m_new);
+    m_use = m_new;
+    l *= f;
+    const uint64_t f2 = f2pack(f, f);
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t o[32];
+      tmem_ld32(o_tmem + c * 32, o);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 32; e += 2) {
+        float a, b;
+        f2unpack(mul2(f2pack(__uint_as_float(o[e]), __uint_as_float(o[e + 1])), f2), a, b);
+        o[e] = __float_as_uint(a);
+        o[e + 1] = __float_as_uint(b);
+      }
+      tmem_st32(o_tmem + c * 32, o);
+    }
+  };
+  // a quarter of the block: 32 keys -> 16 packed columns
+  auto quarter = [&](int qt, uint32_t (&pk)[16], uint64_t& sum_a, uint64_t& sum_b) {
+    const float neg = (m_use == -INFINITY) ? 0.f : -m_use;
+    const uint64_t sc2 = f2pack(sc, sc), neg2 = f2pack(neg, neg);
+#pragma unroll
+    for (int e = 0; e < 16; e += 4) {
+      // 8 scores = 4 pairs per step; the last EMU pairs go to the FMA pipe, the rest to the MUFU
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const int k = qt * 32 + (e + g) * 2;
+        const uint64_t x2 = fma2(f2pack(__uint_as_float(s[k]), __uint_as_float(s[k + 1])), sc2, neg2);
+        float p0, p1;
+        if (g >= 4 - EMU) {
+          ex2_emulated(x2, p0, p1);
+        } else {
+          float x0, x1;
+          f2unpack(x2, x0, x1);
+          p0 = ex2(x0);
+          p1 = ex2(x1);
+        }
+        if (g & 1)
+          sum_b = add2(sum_b, f2pack(p0, p1));
+        else
+          sum_a = add2(sum_a, f2pack(p0, p1));
+        pk[e + g] = pack16<BF16>(p0, p1);
+      }
+    }
+  };
+
+  {
+    const float m_new = fmaxf(m_use, row_max());
+    if (first)
+      m_use = m_new;
+    else if (__any_sync(0xffffffffu, (m_new - m_use) > kRescaleThreshold))
+      rescale_to(m_new);
+  }
+  uint64_t sum_a = f2pack(0.f, 0.f), sum_b = f2pack(0.f, 0.f);
+#pragma unroll
+  for (int qt = 0; qt < 4; ++qt) {
+    uint32_t pk[16];
+    quarter(qt, pk, sum_a, sum_b);
+    tmem_st16(s_tmem + qt * 16, pk);
+    // hand the finished piece to the MMA warp (the last piece goes through p_ready below)
+    if (qt < 3 && (qt + 1) % (4 / kPParts) == 0) {
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&p_part_i[((qt + 1) / (4 / kPParts) - 1) * 2]);
+    }
+  }
+  tmem_st_wait();
+  tc_fence_before();
+  mbar_arrive(p_ready_i);
+  float a, b;
+  f2unpack(add2(sum_a, sum_b), a, b);
+  l += a + b;
+}
+
+
 // EMU: how many of every 4 score pairs take their exponentials on the FMA pipe (0, 1 or 2).
 template <int D, bool BF16, int EMU>
 __global__ void __launch_bounds__(kFmhaThreads, 1)
@@ -387,6 +500,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int q = q0[i] + row;
       // last visible key index for this row
       const int lim_row = p.causal ? min(q + off, p.kv_len - 1) : p.kv_len - 1;
+      // smallest such index over the rows of the tile: blocks reaching beyond it have masked keys
+      const int tile_min_lim = p.causal ? min(q0[i] + off, p.kv_len - 1) : p.kv_len - 1;
       float m_use = -INFINITY;
       float l = 0.f;
       bool ok = true;
@@ -397,101 +512,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           break;
         }
         tc_fence_after();
-        uint32_t s[128];
-        tmem_ld32(s_tmem + 0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-        tmem_ld32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-        tmem_ld32(s_tmem + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
-        tmem_ld32(s_tmem + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
-        tmem_ld_wait();
         const int k0 = j * kTile;
-        // does any row of this tile see a masked key in this block?
-        const int tile_min_lim = p.causal ? min(q0[i] + off, p.kv_len - 1) : p.kv_len - 1;
-        if (k0 + kTile - 1 > tile_min_lim) {
-          const int lim = lim_row - k0;  // keys with local index > lim are masked
-#pragma unroll
-          for (int k = 0; k < 128; ++k)
-            if (k > lim) s[k] = 0xff800000u;  // -inf
-        }
-        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-        for (int k = 0; k < 128; k += 8) {
-          mx0 = max3(mx0, __uint_as_float(s[k + 0]), __uint_as_float(s[k + 1]));
-          mx1 = max3(mx1, __uint_as_float(s[k + 2]), __uint_as_float(s[k + 3]));
-          mx2 = max3(mx2, __uint_as_float(s[k + 4]), __uint_as_float(s[k + 5]));
-          mx3 = max3(mx3, __uint_as_float(s[k + 6]), __uint_as_float(s[k + 7]));
-        }
-        const float m_new = fmaxf(m_use, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc);
-        if (j == 0) {
-          m_use = m_new;
-        } else {
-          const bool need = (m_new - m_use) > kRescaleThreshold;
-          if (__any_sync(0xffffffffu, need)) {
-            const float f = (m_new == -INFINITY) ? 1.f : ex2(m_use - m_new);
-            m_use = m_new;
-            l *= f;
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-              uint32_t o[32];
-              tmem_ld32(o_tmem + c * 32, o);
-              tmem_ld_wait();
-              const uint64_t f2 = f2pack(f, f);
-#pragma unroll
-              for (int e = 0; e < 32; e += 2) {
-                float a, b;
-                f2unpack(mul2(f2pack(__uint_as_float(o[e]), __uint_as_float(o[e + 1])), f2), a, b);
-                o[e] = __float_as_uint(a);
-                o[e + 1] = __float_as_uint(b);
-              }
-              tmem_st32(o_tmem + c * 32, o);
-            }
-          }
-        }
-        const float neg = (m_use == -INFINITY) ? 0.f : -m_use;
-        const uint64_t sc2 = f2pack(sc, sc), neg2 = f2pack(neg, neg);
-        uint64_t sum_a = f2pack(0.f, 0.f), sum_b = f2pack(0.f, 0.f);
-#pragma unroll
-        for (int qt = 0; qt < 4; ++qt) {
-          // a quarter of the block: 32 keys -> 16 packed columns
-          uint32_t pk[16];
-#pragma unroll
-          for (int e = 0; e < 16; e += 4) {
-            // 8 scores = 4 pairs per step; the last EMU pairs go to the FMA pipe, the rest to the MUFU
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const int k = qt * 32 + (e + g) * 2;
-              const uint64_t x2 = fma2(f2pack(__uint_as_float(s[k]), __uint_as_float(s[k + 1])), sc2, neg2);
-              float p0, p1;
-              if (g >= 4 - EMU) {
-                ex2_emulated(x2, p0, p1);
-              } else {
-                float x0, x1;
-                f2unpack(x2, x0, x1);
-                p0 = ex2(x0);
-                p1 = ex2(x1);
-              }
-              if (g & 1)
-                sum_b = add2(sum_b, f2pack(p0, p1));
-              else
-                sum_a = add2(sum_a, f2pack(p0, p1));
-              pk[e + g] = pack16<BF16>(p0, p1);
-            }
-          }
-          tmem_st16(s_tmem + qt * 16, pk);
-          // hand the finished piece to the MMA warp (the last piece goes through p_ready below)
-          if (qt < 3 && (qt + 1) % (4 / kPParts) == 0) {
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(&p_part[((qt + 1) / (4 / kPParts) - 1) * 2 + i]);
-          }
-        }
-        tmem_st_wait();
-        tc_fence_before();
-        mbar_arrive(&p_ready[i]);
-        {
-          float a, b;
-          f2unpack(add2(sum_a, sum_b), a, b);
-          l += a + b;
-        }
+        softmax_block<D, BF16, EMU>(s_tmem, o_tmem, j == 0, k0 + kTile - 1 > tile_min_lim, lim_row - k0, sc, m_use, l,
+                                    &p_part[i], &p_ready[i]);
       }
 
       // ------------------------------ epilogue ------------------------------
@@ -872,99 +895,9 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         }
         ++sn;
         tc_fence_after();
-        uint32_t s[128];
-        tmem_ld32(s_tmem + 0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-        tmem_ld32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-        tmem_ld32(s_tmem + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
-        tmem_ld32(s_tmem + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
-        tmem_ld_wait();
         const int k0 = j * kTile;
-        if (k0 + kTile - 1 > tile_min_lim) {
-          const int lim = lim_row - k0;
-#pragma unroll
-          for (int k = 0; k < 128; ++k)
-            if (k > lim) s[k] = 0xff800000u;
-        }
-        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-        for (int k = 0; k < 128; k += 8) {
-          mx0 = max3(mx0, __uint_as_float(s[k + 0]), __uint_as_float(s[k + 1]));
-          mx1 = max3(mx1, __uint_as_float(s[k + 2]), __uint_as_float(s[k + 3]));
-          mx2 = max3(mx2, __uint_as_float(s[k + 4]), __uint_as_float(s[k + 5]));
-          mx3 = max3(mx3, __uint_as_float(s[k + 6]), __uint_as_float(s[k + 7]));
-        }
-        const float m_new = fmaxf(m_use, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc);
-        if (j == 0) {
-          m_use = m_new;
-        } else {
-          const bool need = (m_new - m_use) > kRescaleThreshold;
-          if (__any_sync(0xffffffffu, need)) {
-            const float f = (m_new == -INFINITY) ? 1.f : ex2(m_use - m_new);
-            m_use = m_new;
-            l *= f;
-            const uint64_t f2 = f2pack(f, f);
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-              uint32_t o[32];
-              tmem_ld32(o_tmem + c * 32, o);
-              tmem_ld_wait();
-#pragma unroll
-              for (int e = 0; e < 32; e += 2) {
-                float a, bb;
-                f2unpack(mul2(f2pack(__uint_as_float(o[e]), __uint_as_float(o[e + 1])), f2), a, bb);
-                o[e] = __float_as_uint(a);
-                o[e + 1] = __float_as_uint(bb);
-              }
-              tmem_st32(o_tmem + c * 32, o);
-            }
-          }
-        }
-        const float neg = (m_use == -INFINITY) ? 0.f : -m_use;
-        const uint64_t sc2 = f2pack(sc, sc), neg2 = f2pack(neg, neg);
-        uint64_t sum_a = f2pack(0.f, 0.f), sum_b = f2pack(0.f, 0.f);
-#pragma unroll
-        for (int qt = 0; qt < 4; ++qt) {
-          // a quarter of the block: 32 keys -> 16 packed columns
-          uint32_t pk[16];
-#pragma unroll
-          for (int e = 0; e < 16; e += 4) {
-            // 8 scores = 4 pairs per step; the last EMU pairs go to the FMA pipe, the rest to the MUFU
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const int k = qt * 32 + (e + g) * 2;
-              const uint64_t x2 = fma2(f2pack(__uint_as_float(s[k]), __uint_as_float(s[k + 1])), sc2, neg2);
-              float p0, p1;
-              if (g >= 4 - EMU) {
-                ex2_emulated(x2, p0, p1);
-              } else {
-                float x0, x1;
-                f2unpack(x2, x0, x1);
-                p0 = ex2(x0);
-                p1 = ex2(x1);
-              }
-              if (g & 1)
-                sum_b = add2(sum_b, f2pack(p0, p1));
-              else
-                sum_a = add2(sum_a, f2pack(p0, p1));
-              pk[e + g] = pack16<BF16>(p0, p1);
-            }
-          }
-          tmem_st16(s_tmem + qt * 16, pk);
-          // hand the finished piece to the MMA warp (the last piece goes through p_ready below)
-          if (qt < 3 && (qt + 1) % (4 / kPParts) == 0) {
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(&p_part[((qt + 1) / (4 / kPParts) - 1) * 2 + i]);
-          }
-        }
-        tmem_st_wait();
-        tc_fence_before();
-        mbar_arrive(&p_ready[i]);
-        {
-          float a, bb;
-          f2unpack(add2(sum_a, sum_b), a, bb);
-          l += a + bb;
-        }
+        softmax_block<D, BF16, EMU>(s_tmem, o_tmem, j == 0, k0 + kTile - 1 > tile_min_lim, lim_row - k0, sc, m_use, l,
+                                    &p_part[i], &p_ready[i]);
       }
       if (!ok) break;
 
