@@ -176,3 +176,26 @@ def test_kernel_variants_agree(cuda_device, variant):
     o = fmha.fmha_fwd(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), causal=False, variant=variant)
     ref = oracle.fmha_ref(q, k, v)
     assert oracle.max_abs(o, ref) <= _tol(torch.bfloat16, ref)
+
+
+@pytest.mark.parametrize("variant", [2, 12])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_rising_row_maximum(cuda_device, variant, D, dtype):
+    """Keys whose magnitude grows along the sequence: the running row maximum climbs by far more than
+    the lazy-rescale threshold (2^8), in steps small and large, so both kernels' rescale path (O and l
+    scaled in place) runs many times per row.
+    Non-causal and causal, the causal case with the ragged tail masked."""
+    from b200k import fmha, inputs
+    S = 1500
+    q, k, v = inputs.fmha_inputs(1, 4, 2, S, S, D, dtype, seed=91 + D)
+    ramp = torch.linspace(0.05, 6.0, S).view(1, 1, S, 1)
+    ramp[:, :, 640:] *= 2.5  # one large jump in the middle of a block
+    k = (k.float() * ramp).to(dtype)
+    for causal in (False, True):
+        o = fmha.fmha_fwd(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), causal=causal, variant=variant)
+        ref = oracle.fmha_ref(q, k, v, causal=causal)
+        assert not torch.isnan(o).any()
+        # the softmax is nearly one-hot here, so |o| reaches several units: allow the output's own
+        # rounding (half an ulp at max|o|: 2^-11 relative in fp16) on top of the stated tolerance
+        assert oracle.max_abs(o, ref) <= _tol(dtype, ref) + float(ref.abs().max()) * 2.0 ** -10

@@ -43,6 +43,14 @@ constexpr int kFmhaThreads = 384;  // 2 softmax warpgroups + 1 warpgroup holding
 constexpr int kTile = 128;  // query rows per tile and keys per block
 constexpr float kRescaleThreshold = 8.0f;
 constexpr int kDefaultEmu = 1;
+// Register split by role (setmaxnreg).  setmaxnreg.inc waits until the CTA's pool - the registers it
+// was launched with: threads x the per-thread count ptxas chose under __launch_bounds__, a multiple
+// of 8 - has room, and waits for ever if the roles' claims add up to more than that pool, so every
+// split is checked against it at compile time.
+constexpr int kAuxRegs = 56, kSoftmaxRegs = 224;
+constexpr int launch_regs(int threads) { return 65536 / threads / 8 * 8 > 255 ? 255 : 65536 / threads / 8 * 8; }
+static_assert(256 * kSoftmaxRegs + 128 * kAuxRegs <= kFmhaThreads * launch_regs(kFmhaThreads),
+              "one-item kernel: register claims exceed the launch pool");
 #ifndef B200K_FMHA_P_PARTS
 #define B200K_FMHA_P_PARTS 2
 #endif
@@ -358,10 +366,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (warp >= 10) {
     // idle warps of the third warpgroup
-    reg_dealloc<56>();
+    reg_dealloc<kAuxRegs>();
   } else if (warp == 8) {
     // ------------------------------- TMA loader -------------------------------
-    reg_dealloc<56>();
+    reg_dealloc<kAuxRegs>();
     if (elect_one() && nb_max > 0) {
       auto load_tile = [&](const CUtensorMap* tm, uint8_t* dst, uint64_t* bar, int row, int head) {
         mbar_expect_tx(bar, L::kTileBytes);
@@ -393,7 +401,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (warp == 9) {
     // ------------------------------- MMA issuer -------------------------------
-    reg_dealloc<56>();
+    reg_dealloc<kAuxRegs>();
     if (elect_one() && nb_max > 0) {
       constexpr uint32_t idesc_s = make_idesc_f16(BF16 ? 1 : 0, 0, 0, kTile, kTile);
       constexpr uint32_t idesc_pv = make_idesc_f16(BF16 ? 1 : 0, 0, 1, kTile, D);
@@ -489,7 +497,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else {
     // ----------------------------- softmax groups -----------------------------
-    reg_alloc<224>();
+    reg_alloc<kSoftmaxRegs>();
     const int i = warp >> 2;             // tile of this group
     const int row = threadIdx.x & 127;   // query row inside the tile = TMEM lane
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
@@ -581,6 +589,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // Register split of the persistent kernel (per thread; 256 softmax threads + 128 others must fit the
 // 64K registers of the SM): its loader and MMA threads carry more running state than in the one-item kernel.
 constexpr int kPersistAuxRegs = 88, kPersistSoftmaxRegs = 208;
+static_assert(256 * kPersistSoftmaxRegs + 128 * kPersistAuxRegs <= kFmhaThreads * launch_regs(kFmhaThreads),
+              "persistent kernel: register claims exceed the launch pool");
 
 template <int D>
 struct FmhaPSmem {
