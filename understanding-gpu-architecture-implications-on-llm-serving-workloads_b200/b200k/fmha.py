@@ -70,11 +70,19 @@ def decode_workspace(B: int, Hq: int, Hkv: int, Sq: int, Skv: int, D: int, num_s
     return torch.empty(max(int(n), 16), dtype=torch.uint8, device=device)
 
 
+def decode_static_fits(B: int, Hq: int, Hkv: int, Sq: int, Skv: int, D: int) -> bool:
+    """Whether the allocation-free decode entry point can take this problem (its unsplit partials
+    must fit the scratch array built into the library)."""
+    return B * Hq * Sq * (D + 2) * 4 <= int(_lib.lib().b200k_fmha_decode_static_scratch_bytes())
+
+
 def fmha_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_lens: torch.Tensor | None = None,
                 num_splits: int = 0, scale: float | None = None, out: torch.Tensor | None = None,
-                workspace: torch.Tensor | None = None) -> torch.Tensor:
+                workspace: torch.Tensor | None = None, static_scratch: bool = False) -> torch.Tensor:
     """Split-KV attention for decode-shaped inputs (q [B,Hq,Sq,D] with small Sq, normally 1).
-    kv_lens: int32 [B] on the device (valid keys of each sequence) or None for all of Skv."""
+    kv_lens: int32 [B] on the device (valid keys of each sequence) or None for all of Skv.
+    static_scratch: use the entry point that keeps its partials in the library's built-in scratch
+    array instead of a workspace tensor (nothing is allocated; for callers inside a graph capture)."""
     _check_qkv(q, k, v)
     B, Hq, Sq, D = q.shape
     Hkv, Skv = k.size(1), k.size(2)
@@ -93,6 +101,14 @@ def fmha_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_lens: torc
         scale = 1.0 / math.sqrt(D)
     L = _lib.lib()
     with torch.cuda.device(q.device):
+        if static_scratch:
+            code = L.b200k_fmha_decode_splitkv_static(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, Hq, Hkv, Sq, Skv, D,
+                _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(out), float(scale),
+                kv_lens.data_ptr() if kv_lens is not None else None, int(num_splits), _DTYPES[q.dtype],
+                torch.cuda.current_stream(q.device).cuda_stream)
+            _lib.check(code, "b200k_fmha_decode_splitkv_static")
+            return out
         if workspace is None:
             workspace = decode_workspace(B, Hq, Hkv, Sq, Skv, D, num_splits, q.device)
         code = L.b200k_fmha_decode_splitkv(

@@ -19,6 +19,12 @@ library:
     o_proj, down_proj   GEMM with the residual add fused into the epilogue
     gate/up one GEMM over the column-interleaved weight with SiLU(gate)*up fused
 `--baseline` times the same stack with torch.matmul and scaled_dot_product_attention.
+
+Decode steps are launch-bound from Python (about ten small kernels per layer), so by default the
+step is captured once in a CUDA graph and replayed (`--no-graph` keeps the eager loop): position,
+per-sequence lengths and the token fed back all live in device tensors that the captured step
+updates in place, the cache write is an index_copy_ at the device-side position, and the decode
+attention runs on the library's allocation-free entry point, so a replay touches no host state.
 """
 from __future__ import annotations
 
@@ -153,6 +159,88 @@ class SyntheticLlama:
         x = _rms_norm(x.view(B, S, -1)[:, -1], self.norm_f, c.rms_eps)
         return self._mm(x.contiguous(), self.lm_head)
 
+    def _decode_step(self, st: dict) -> None:
+        """One greedy decode step with all step state on the device (capturable in a CUDA graph):
+        st["tok"] [B,1] is consumed and overwritten with the next token, st["pos"] (int64 [1]) and
+        st["lens"] (int32 [B]) advance by one, the new token is also written to st["out"][:, pos+1]."""
+        c = self.cfg
+        tok, pos, lens = st["tok"], st["pos"], st["lens"]
+        B = tok.size(0)
+        D, Hq, Hkv = c.head_dim, c.n_heads, c.n_kv_heads
+        x = self.embed.index_select(0, tok.reshape(-1))
+        cos, sin = self._angles(pos.view(1, 1).expand(B, 1))
+        lens.add_(1)  # the key written below counts
+        for li, layer in enumerate(self.layers):
+            h = _rms_norm(x, layer["norm1"], c.rms_eps)
+            qkv = self._mm(h, layer["wqkv"]).view(B, 1, Hq + 2 * Hkv, D)
+            q = _rope(qkv[:, :, :Hq], cos, sin)
+            k = _rope(qkv[:, :, Hq:Hq + Hkv], cos, sin)
+            v = qkv[:, :, Hq + Hkv:]
+            kc, vc = self.k_cache[li], self.v_cache[li]
+            kc.index_copy_(2, pos, k.transpose(1, 2))
+            vc.index_copy_(2, pos, v.transpose(1, 2))
+            attn = torch.empty((B, 1, Hq, D), dtype=self.dtype, device=self.device)
+            av = attn.transpose(1, 2)
+            if self.lib:
+                fmha.fmha_decode(q.transpose(1, 2), kc, vc, kv_lens=lens, out=av, static_scratch=st["static_scratch"])
+            else:
+                # comparator: lengths are uniform here, so the valid prefix is a mask over the padded cache
+                mask = (torch.arange(kc.size(2), device=self.device)[None, :] < lens[:, None].long())[:, None, None, :]
+                av.copy_(F.scaled_dot_product_attention(q.transpose(1, 2), kc, vc, attn_mask=mask, enable_gqa=Hq != Hkv))
+            x = self._mm_add(attn.view(B, Hq * D), layer["wo"], x)
+            h = _rms_norm(x, layer["norm2"], c.rms_eps)
+            x = self._mm_add(self._mlp_in(h, layer), layer["w_down"], x)
+        x = _rms_norm(x, self.norm_f, c.rms_eps)
+        nxt = self._mm(x.contiguous(), self.lm_head).argmax(-1, keepdim=True)
+        pos.add_(1)
+        st["out"].index_copy_(1, pos, nxt)
+        tok.copy_(nxt)
+
+    @torch.no_grad()
+    def generate_graphed(self, prompt: torch.Tensor, gen_len: int):
+        """Greedy decoding with the decode step captured in a CUDA graph; same return values as
+        `generate`.  The capture (and its warm-up step on a side stream) happens before the timed
+        region and leaves the step state untouched: it runs on scratch copies of the state."""
+        B, S = prompt.shape
+        self.alloc_cache(B, S + gen_len)
+        dev = self.device
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        out = torch.zeros((B, S + gen_len), dtype=torch.long, device=dev)
+        out[:, :S] = prompt
+        st = {"tok": torch.zeros((B, 1), dtype=torch.long, device=dev), "pos": torch.zeros(1, dtype=torch.long, device=dev),
+              "lens": torch.zeros(B, dtype=torch.int32, device=dev), "out": out,
+              "static_scratch": self.lib and fmha.decode_static_fits(B, self.cfg.n_heads, self.cfg.n_kv_heads, 1,
+                                                                      S + gen_len, self.cfg.head_dim)}
+
+        def reset(first_tok):
+            st["tok"].copy_(first_tok)
+            st["pos"].fill_(S)      # position of the token in st["tok"]
+            st["lens"].fill_(S)     # keys in the cache before that token is appended
+        graph = None
+        if gen_len > 1:
+            # capture on dummy state (token 0 at position S): the cache slot it writes is rewritten by the real step
+            reset(torch.zeros((B, 1), dtype=torch.long, device=dev))
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self._decode_step(st)
+            torch.cuda.current_stream().wait_stream(side)
+            reset(torch.zeros((B, 1), dtype=torch.long, device=dev))
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._decode_step(st)
+            torch.cuda.synchronize()
+        e[0].record()
+        nxt = self.forward(prompt, 0).argmax(-1, keepdim=True)
+        e[1].record()
+        out[:, S:S + 1] = nxt
+        reset(nxt)
+        for _ in range(1, gen_len):
+            graph.replay()
+        e[2].record()
+        torch.cuda.synchronize()
+        return out, e[0].elapsed_time(e[1]) / 1e3, e[1].elapsed_time(e[2]) / 1e3
+
     @torch.no_grad()
     def generate(self, prompt: torch.Tensor, gen_len: int):
         """Greedy decoding; returns (tokens [B, prompt+gen], prefill seconds, decode seconds) timed with
@@ -173,14 +261,17 @@ class SyntheticLlama:
         return torch.cat(out, dim=1), e[0].elapsed_time(e[1]) / 1e3, e[1].elapsed_time(e[2]) / 1e3
 
 
-def run(cfg: LlamaConfig, batch: int, prompt_len: int, gen_len: int, use_library: bool, dtype=torch.bfloat16) -> dict:
+def run(cfg: LlamaConfig, batch: int, prompt_len: int, gen_len: int, use_library: bool, dtype=torch.bfloat16,
+        graph: bool = True) -> dict:
     model = SyntheticLlama(cfg, dtype=dtype, use_library=use_library)
     g = torch.Generator(device=model.device).manual_seed(1)
     prompt = torch.randint(0, cfg.vocab, (batch, prompt_len), generator=g, device=model.device)
-    model.generate(prompt[:, :min(prompt_len, 128)], 2)  # warm-up (allocator, first-call set-up)
-    toks, t_prefill, t_decode = model.generate(prompt, gen_len)
+    gen = model.generate_graphed if graph else model.generate
+    gen(prompt[:, :min(prompt_len, 128)], 2)  # warm-up (allocator, first-call set-up)
+    toks, t_prefill, t_decode = gen(prompt, gen_len)
     assert toks.shape == (batch, prompt_len + gen_len)
-    return {"impl": "b200k" if use_library else "torch", "layers": cfg.n_layers, "batch": batch,
+    return {"impl": "b200k" if use_library else "torch", "decode": "cuda graph" if graph else "eager",
+            "layers": cfg.n_layers, "batch": batch,
             "prompt_len": prompt_len, "gen_len": gen_len, "prefill_s": t_prefill,
             "prefill_tok_s": batch * prompt_len / t_prefill, "decode_s": t_decode,
             "decode_tok_s": batch * (gen_len - 1) / max(t_decode, 1e-9),
@@ -195,12 +286,13 @@ def main(argv=None):
     ap.add_argument("--gen-len", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=32)
     ap.add_argument("--baseline", action="store_true", help="also time the torch.matmul / SDPA version")
+    ap.add_argument("--no-graph", action="store_true", help="eager decode loop instead of the captured step")
     args = ap.parse_args(argv)
     cfg = LlamaConfig(n_layers=args.layers, n_kv_heads=args.kv_heads)
-    print(json.dumps(run(cfg, args.batch, args.prompt_len, args.gen_len, True)), flush=True)
+    print(json.dumps(run(cfg, args.batch, args.prompt_len, args.gen_len, True, graph=not args.no_graph)), flush=True)
     if args.baseline:
         torch.cuda.empty_cache()
-        print(json.dumps(run(cfg, args.batch, args.prompt_len, args.gen_len, False)), flush=True)
+        print(json.dumps(run(cfg, args.batch, args.prompt_len, args.gen_len, False, graph=not args.no_graph)), flush=True)
     return 0
 
 

@@ -17,6 +17,10 @@
 //     to its own shared memory (the drained stage buffers), the cluster synchronises, and CTA r
 //     sums its share of the columns of all S tiles through distributed shared memory in rank
 //     order 0..S-1 (bit-identical from run to run), converts and stores its part of C.
+//   * The same final step carries the fused epilogues of the wide kernels (EPI: 0 none, 1 residual
+//     add in fp32 before rounding, 2 SiLU(gate)*up over interleaved column pairs, output N/2 wide),
+//     so the o_proj / down_proj / gate-up projections of a decode step stream their weights the
+//     same way.
 //
 // Reference contract: kernels/gemm/pkg/gemm_unified/csrc/auto/gemm_0.cu:12-20.  The
 // reference's tensor-core rungs cannot run these shapes at all (no bounds checks, M % 128
@@ -62,6 +66,22 @@ __device__ __forceinline__ float4 ld_dsmem_f4(uint32_t cluster_addr) {
   return v;
 }
 template <bool BF16>
+__device__ __forceinline__ void unpack2s(uint32_t u, float& lo, float& hi) {
+  if constexpr (BF16) {
+    const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&u);
+    lo = __low2float(h);
+    hi = __high2float(h);
+  } else {
+    const __half2 h = *reinterpret_cast<const __half2*>(&u);
+    lo = __low2float(h);
+    hi = __high2float(h);
+  }
+}
+// same formula as the wide kernels' SwiGLU epilogue
+__device__ __forceinline__ float silu_mul_s(float gate, float up) {
+  return __fdividef(gate, 1.f + __expf(-gate)) * up;
+}
+template <bool BF16>
 __device__ __forceinline__ uint32_t pack2s(float lo, float hi) {
   if constexpr (BF16) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -72,10 +92,11 @@ __device__ __forceinline__ uint32_t pack2s(float lo, float hi) {
   }
 }
 
-template <int MPAD, bool BF16>
+template <int MPAD, bool BF16, int EPI>
 __global__ void __launch_bounds__(kSkThreads, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
-                   uint16_t* __restrict__ C, int64_t ldc, int M, int N, int K, int* status) {
+                   uint16_t* __restrict__ C, int64_t ldc, int M, int N, int K, int* status,
+                   const uint16_t* __restrict__ R, int64_t ldr) {
   using L = SkinnySmem<MPAD>;
   constexpr int kStages = L::kStages;
   constexpr uint32_t kAccCols = MPAD < 32 ? 32 : MPAD;  // TMEM columns of one accumulator
@@ -236,10 +257,26 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         acc.z += v.z;
         acc.w += v.w;
       }
-      uint2 o;
-      o.x = pack2s<BF16>(acc.x, acc.y);
-      o.y = pack2s<BF16>(acc.z, acc.w);
-      *reinterpret_cast<uint2*>(C + (int64_t)row * ldc + n) = o;
+      if constexpr (EPI == 2) {
+        // columns n..n+3 are (gate, up), (gate, up) of outputs n/2 and n/2+1
+        *reinterpret_cast<uint32_t*>(C + (int64_t)row * ldc + n / 2) =
+            pack2s<BF16>(silu_mul_s(acc.x, acc.y), silu_mul_s(acc.z, acc.w));
+      } else {
+        if constexpr (EPI == 1) {
+          const uint2 r2 = *reinterpret_cast<const uint2*>(R + (int64_t)row * ldr + n);
+          float lo, hi;
+          unpack2s<BF16>(r2.x, lo, hi);
+          acc.x += lo;
+          acc.y += hi;
+          unpack2s<BF16>(r2.y, lo, hi);
+          acc.z += lo;
+          acc.w += hi;
+        }
+        uint2 o;
+        o.x = pack2s<BF16>(acc.x, acc.y);
+        o.y = pack2s<BF16>(acc.z, acc.w);
+        *reinterpret_cast<uint2*>(C + (int64_t)row * ldc + n) = o;
+      }
     }
   }
 
@@ -270,11 +307,11 @@ int skinny_cluster_size(int N, int K) {
   return s;
 }
 
-template <int MPAD, bool BF16>
+template <int MPAD, bool BF16, int EPI>
 static int launch_skinny_t(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
-                           int64_t ldc, cudaStream_t stream) {
+                           int64_t ldc, cudaStream_t stream, const void* R, int64_t ldr) {
   using L = SkinnySmem<MPAD>;
-  auto kfn = gemm_skinny_kernel<MPAD, BF16>;
+  auto kfn = gemm_skinny_kernel<MPAD, BF16, EPI>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -316,7 +353,8 @@ static int launch_skinny_t(const void* A, const void* B, void* C, int M, int N, 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kfn, tmX, tmW, reinterpret_cast<uint16_t*>(C), ldc, M, N, K, status);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kfn, tmX, tmW, reinterpret_cast<uint16_t*>(C), ldc, M, N, K, status,
+                                     reinterpret_cast<const uint16_t*>(R), ldr);
   count_launch();
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
@@ -326,16 +364,19 @@ static int launch_skinny_t(const void* A, const void* B, void* C, int M, int N, 
 }
 
 int launch_skinny(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
-                  bool bf16, cudaStream_t stream) {
-  if (M > 128) return B200K_ESHAPE;
-#define B200K_SKINNY(MP)                                                                       \
-  return bf16 ? launch_skinny_t<MP, true>(A, B, C, M, N, K, lda, ldb, ldc, stream)              \
-              : launch_skinny_t<MP, false>(A, B, C, M, N, K, lda, ldb, ldc, stream)
+                  bool bf16, cudaStream_t stream, int epilogue, const void* R, int64_t ldr) {
+  if (M > 128 || epilogue < 0 || epilogue > 2) return B200K_ESHAPE;
+#define B200K_SKINNY_E(MP, EP)                                                                         \
+  (bf16 ? launch_skinny_t<MP, true, EP>(A, B, C, M, N, K, lda, ldb, ldc, stream, R, ldr)                \
+        : launch_skinny_t<MP, false, EP>(A, B, C, M, N, K, lda, ldb, ldc, stream, R, ldr))
+#define B200K_SKINNY(MP) \
+  return epilogue == 0 ? B200K_SKINNY_E(MP, 0) : epilogue == 1 ? B200K_SKINNY_E(MP, 1) : B200K_SKINNY_E(MP, 2)
   if (M <= 16) { B200K_SKINNY(16); }
   if (M <= 32) { B200K_SKINNY(32); }
   if (M <= 64) { B200K_SKINNY(64); }
   B200K_SKINNY(128);
 #undef B200K_SKINNY
+#undef B200K_SKINNY_E
 }
 
 }  // namespace b200k

@@ -616,6 +616,9 @@ extern "C" int b200k_gemm_fused(const void* A, const void* B, void* C, const voi
   const long pair_tiles = (long)((M + 255) / 256) * ((N + 255) / 256);
   const bool big = pair_tiles >= sms / 2;
   const bool bf16 = dtype == B200K_BF16;
+  // decode-shaped calls stream the weight like the plain skinny GEMM (same rule as b200k_gemm's AUTO)
+  if (M <= 32 || (M <= 128 && (N + 127) / 128 < 64))
+    return launch_skinny(A, B, C, M, N, K, lda, ldb, ldc, bf16, stream, epilogue, R, ldr);
 #define B200K_FUSED(EP)                                                                                       \
   (big ? (bf16 ? launch_tc<2, 256, 6, true, EP>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream, R, ldr)         \
                : launch_tc<2, 256, 6, false, EP>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream, R, ldr))       \

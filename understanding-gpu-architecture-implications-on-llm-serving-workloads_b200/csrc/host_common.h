@@ -34,8 +34,9 @@ struct DevInfo {
 const DevInfo& dev_info();
 
 // Skinny GEMM (M <= 128): split-K inside thread-block clusters (gemm_skinny_sm100.cu).
+// epilogue: 0 none, B200K_EPI_ADD (R, ldr: the residual), B200K_EPI_SWIGLU (C is N/2 wide).
 int launch_skinny(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
-                  bool bf16, cudaStream_t stream);
+                  bool bf16, cudaStream_t stream, int epilogue = 0, const void* R = nullptr, int64_t ldr = 0);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
