@@ -5,18 +5,22 @@
 //   * Operands are swapped for the tensor core: the 128 weight columns of a slab are the MMA's
 //     M rows (A operand, MN-major because B[K,N] is contiguous along N) and the activation rows
 //     are the MMA's N columns (B operand, K-major), padded only to MPAD in {16, 32, 64, 128}.
-//     A stage is 32 KB of weights (256 columns: 512 contiguous bytes of every k-row, which
-//     keeps DRAM pages open longer than 128-byte pieces) plus MPAD*128 bytes of activations,
-//     so small M leaves room for more weight bytes in flight (6 stages at M <= 16).
-//   * One 256-column slab of B per cluster of S CTAs (S in 1..8, about 96 CTAs in all);
-//     CTA r of the cluster streams k-blocks [r*nkb/S, (r+1)*nkb/S): split-K in a cluster.
-//   * Roles per CTA: a TMA warp, one MMA thread (two tcgen05.mma M = 128, N = MPAD, K = 16 per
-//     k-step, accumulators D[weight column][activation row] in 2 x MPAD TMEM columns), four
-//     warps that drain.
-//   * The split-K partials never go to HBM: every CTA writes its fp32 partial tile [row][256]
+//     A stage is 64 k-rows of the slab (16 or 32 KB of weights: 256 or 512 contiguous bytes of
+//     every k-row) plus MPAD*128 bytes of activations, as many stages as fit (up to 8), so small M
+//     leaves room for more weight bytes in flight.
+//   * One slab of B (128 columns when the slabs fit one wave of CTAs, else 256) per cluster of S CTAs
+//     (S in 1..8, 96..128 CTAs in all); CTA r of the cluster streams k-blocks
+//     [r*nkb/S, (r+1)*nkb/S): split-K in a cluster.
+//   * Roles per CTA (12 warps): thread 0 initialises the barriers and at once issues the first ring of
+//     TMA loads, then keeps loading; one MMA thread (tcgen05.mma M = 128, N = MPAD, K = 16, one per
+//     128 weight columns and k-step, accumulators D[weight column][activation row] in TMEM); eight
+//     warps that drain; two more that only help in the final step.  Draining and reducing are
+//     instruction-bound (the streaming loop itself runs at the HBM rate), hence the many warps.
+//   * The split-K partials never go to HBM: every CTA writes its fp32 partial tile [row][slab]
 //     to its own shared memory (the drained stage buffers), the cluster synchronises, and CTA r
 //     sums its share of the columns of all S tiles through distributed shared memory in rank
-//     order 0..S-1 (bit-identical from run to run), converts and stores its part of C.
+//     order 0..S-1 (bit-identical from run to run), converts and stores its part of C.  A cluster
+//     of one needs no cluster barrier and none at exit.
 //   * The same final step carries the fused epilogues of the wide kernels (EPI: 0 none, 1 residual
 //     add in fp32 before rounding, 2 SiLU(gate)*up over interleaved column pairs, output N/2 wide),
 //     so the o_proj / down_proj / gate-up projections of a decode step stream their weights the
@@ -36,20 +40,26 @@
 namespace b200k {
 namespace {
 
-constexpr int kSkBK = 64, kSkThreads = 192;
-constexpr int kSkBN = 256;                        // weight columns per CTA: 512 contiguous bytes per k-row
-constexpr int kSkSub = kSkBN / 128;               // MMAs of 128 weight columns each
-constexpr uint32_t kSkWBytes = kSkBN * kSkBK * 2;  // weight tile of one stage (32 KB)
+constexpr int kSkBK = 64;
+// 12 warps: TMA, MMA, 8 that drain the accumulators, and 2 more that only help in the final reduction
+// (draining and reducing are instruction-bound: measured 2.8 us of a 19 us kernel with 6 warps)
+constexpr int kSkThreads = 384;
+constexpr int kSkDrainGroups = 2;  // groups of four draining warps
+// BN = weight columns per CTA (256 or 128): BN/128 MMAs of 128 weight columns per k-step, a weight
+// tile of BN*64*2 bytes per stage (32 or 16 KB), a partial tile of MPAD*BN floats.
 
-template <int MPAD>
+template <int MPAD, int BN>
 struct SkinnySmem {
+  static constexpr int kSkBN = BN;
+  static constexpr uint32_t kSkWBytes = BN * kSkBK * 2;
   static constexpr uint32_t kXBytes = MPAD * kSkBK * 2;  // activation tile of one stage
   static constexpr uint32_t kStageBytes = kSkWBytes + (kXBytes < 1024 ? 1024 : kXBytes);
-  // one CTA per SM: as many stages as fit in ~208 KB, at most 6
-  static constexpr int kStages = (208 * 1024 / kStageBytes) > 6 ? 6 : (208 * 1024 / kStageBytes);
+  // one CTA per SM: as many stages as fit in ~208 KB, at most 6 (8 with the narrow slab)
+  static constexpr int kMaxStages = BN == 256 ? 6 : 8;
+  static constexpr int kStages = (208 * 1024 / kStageBytes) > kMaxStages ? kMaxStages : (208 * 1024 / kStageBytes);
   static constexpr uint32_t kTileBytes = MPAD * kSkBN * 4;  // fp32 partial tile, reuses the stage buffers
   static constexpr uint32_t kBarOff = kStages * kStageBytes > kTileBytes ? kStages * kStageBytes : kTileBytes;
-  static constexpr uint32_t kTotal = kBarOff + 128 + 1024;
+  static constexpr uint32_t kTotal = kBarOff + 256 + 1024;  // barriers (2 per stage + 1) and the TMEM address, alignment slack
 };
 
 __device__ __forceinline__ uint32_t cluster_size_x() {
@@ -92,13 +102,15 @@ __device__ __forceinline__ uint32_t pack2s(float lo, float hi) {
   }
 }
 
-template <int MPAD, bool BF16, int EPI>
+template <int MPAD, bool BF16, int EPI, int BN>
 __global__ void __launch_bounds__(kSkThreads, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                    uint16_t* __restrict__ C, int64_t ldc, int M, int N, int K, int* status,
                    const uint16_t* __restrict__ R, int64_t ldr) {
-  using L = SkinnySmem<MPAD>;
+  using L = SkinnySmem<MPAD, BN>;
   constexpr int kStages = L::kStages;
+  constexpr int kSkBN = BN, kSkSub = BN / 128;
+  constexpr uint32_t kSkWBytes = L::kSkWBytes;
   constexpr uint32_t kAccCols = MPAD < 32 ? 32 : MPAD;  // TMEM columns of one accumulator
   constexpr uint32_t kTmemCols = kSkSub * kAccCols;
   extern __shared__ uint8_t smem_raw[];
@@ -117,6 +129,22 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
   const int kb_begin = (int)((int64_t)rank * num_kb / S);
   const int kb_end = (int)((int64_t)(rank + 1) * num_kb / S);
 
+  auto load_stage = [&](int kb, uint32_t stage) {
+    uint8_t* sw = smem + stage * L::kStageBytes;
+    uint8_t* sx = sw + kSkWBytes;
+    mbar_expect_tx(&full_bar[stage], kSkWBytes + L::kXBytes);
+#pragma unroll
+    for (int j = 0; j < kSkBN / 64; ++j)
+      tma_load_2d(sw + j * (kSkBK * 128), &tmW, &full_bar[stage], n0 + j * 64, kb * kSkBK);
+    tma_load_2d(sx, &tmX, &full_bar[stage], kb * kSkBK, 0);
+  };
+  // k-blocks whose loads thread 0 issues right after initialising the barriers, while the TMEM
+  // allocation and the CTA-wide sync are still under way (every stage is free at that point)
+  const int kb_pre = min(kb_end, kb_begin + kStages);
+  if (threadIdx.x == 32) {
+    prefetch_tmap(&tmW);
+    prefetch_tmap(&tmX);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -124,8 +152,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     }
     mbar_init(tmem_full, 1);
     fence_mbar_init();
-    prefetch_tmap(&tmX);
-    prefetch_tmap(&tmW);
+    for (int kb = kb_begin; kb < kb_pre; ++kb) load_stage(kb, (uint32_t)(kb - kb_begin));
   }
   if (warp == 1) {
     tmem_alloc<1>(tmem_holder, kTmemCols);
@@ -137,20 +164,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp == 0) {
-    if (elect_one()) {
-      uint32_t stage = 0, phase = 0;
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
+    if (lane == 0) {
+      // the first ring was issued above: continue with the second use of stage 0
+      uint32_t stage = 0, phase = 1;
+      for (int kb = kb_pre; kb < kb_end; ++kb) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
           report_timeout(status, KID_GEMM, ROLE_PRODUCER);
           break;
         }
-        uint8_t* sw = smem + stage * L::kStageBytes;
-        uint8_t* sx = sw + kSkWBytes;
-        mbar_expect_tx(&full_bar[stage], kSkWBytes + L::kXBytes);
-#pragma unroll
-        for (int j = 0; j < kSkBN / 64; ++j)
-          tma_load_2d(sw + j * (kSkBK * 128), &tmW, &full_bar[stage], n0 + j * 64, kb * kSkBK);
-        tma_load_2d(sx, &tmX, &full_bar[stage], kb * kSkBK, 0);
+        load_stage(kb, stage);
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1;
@@ -190,25 +212,38 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       }
       if (ok) umma_commit<1>(tmem_full);
     }
-  } else {
+  } else if (warp < 2 + 4 * kSkDrainGroups) {
     // drain TMEM (lane = weight column, TMEM column = activation row) into this CTA's fp32
-    // tile [row][kSkBN]: consecutive lanes write consecutive words
+    // tile [row][kSkBN]: consecutive lanes write consecutive words.  Two groups of four warps (a warp
+    // reaches the TMEM lanes of quarter warp % 4) take alternate (128-column, row-chunk) pieces.
     const int ew = warp & 3;
+    const int grp = (warp - 2) >> 2;
     const bool have = kb_end > kb_begin;
-    bool ok = true;
-    if (have && !mbar_wait(tmem_full, 0)) {
-      if (lane == 0) report_timeout(status, KID_GEMM, ROLE_EPILOGUE);
-      ok = false;
+    // Only one lane polls the accumulator barrier during the main loop; the other 255 draining threads
+    // park on a hardware named barrier (polling from eight warps cost the loader and the MMA thread
+    // about 10 % of the streaming rate).  The verdict travels through shared memory.
+    volatile uint32_t* verdict = tmem_holder + 1;
+    if (warp == 2 && lane == 0) {
+      uint32_t good = 1;
+      if (have && !mbar_wait(tmem_full, 0)) {
+        report_timeout(status, KID_GEMM, ROLE_EPILOGUE);
+        good = 0;
+      }
+      *verdict = good;
     }
+    named_barrier_sync(1, 128 * kSkDrainGroups);
+    const bool ok = *verdict != 0;
     tc_fence_after();
     float* tile = reinterpret_cast<float*>(smem);
     constexpr int kChunk = MPAD < 32 ? 16 : 32;
+    int piece = 0;
 #pragma unroll 1
     for (int sub = 0; sub < kSkSub; ++sub) {
       const int n = sub * 128 + ew * 32 + lane;
 #pragma unroll 1
-      for (int cb = 0; cb < MPAD / kChunk; ++cb) {
+      for (int cb = 0; cb < MPAD / kChunk; ++cb, ++piece) {
         if (cb * kChunk >= M) break;
+        if (piece % kSkDrainGroups != grp) continue;
         uint32_t v[kChunk];
         if (have && ok) {
           const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + sub * kAccCols + cb * kChunk;
@@ -230,58 +265,83 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     }
   }
 
-  // every CTA's partial tile is complete and visible to the cluster
+  // every CTA's partial tile is complete and visible to the cluster (a cluster of one has no peers:
+  // a CTA-wide barrier is enough, and nothing needs to wait for anybody at the end)
   tc_fence_before();
-  cluster_sync_all();
+  if (S == 1)
+    __syncthreads();
+  else
+    cluster_sync_all();
 
   {
     // this CTA's slice of the tile's 16-byte chunks (any S in 1..8 divides them unevenly at most by one)
     const int c_begin = (int)rank * (kSkBN / 4) / (int)S;
     const int c_end = ((int)rank + 1) * (kSkBN / 4) / (int)S;
     const int w4 = c_end - c_begin;
-    const int items = M * w4;
     const uint32_t tile_addr = smem_u32(smem);
-    for (int item = threadIdx.x; item < items; item += kSkThreads) {
-      const int row = item / w4;
-      const int c = c_begin + item % w4;
-      const int n = n0 + c * 4;
-      if (n >= N) continue;
-      const uint32_t off = (uint32_t)(row * kSkBN + c * 4) * 4u;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (uint32_t s = 0; s < S; ++s) {
-        uint32_t remote;
-        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(tile_addr + off), "r"(s));
-        const float4 v = ld_dsmem_f4(remote);
-        acc.x += v.x;
-        acc.y += v.y;
-        acc.z += v.z;
-        acc.w += v.w;
-      }
-      if constexpr (EPI == 2) {
-        // columns n..n+3 are (gate, up), (gate, up) of outputs n/2 and n/2+1
-        *reinterpret_cast<uint32_t*>(C + (int64_t)row * ldc + n / 2) =
-            pack2s<BF16>(silu_mul_s(acc.x, acc.y), silu_mul_s(acc.z, acc.w));
-      } else {
-        if constexpr (EPI == 1) {
-          const uint2 r2 = *reinterpret_cast<const uint2*>(R + (int64_t)row * ldr + n);
-          float lo, hi;
-          unpack2s<BF16>(r2.x, lo, hi);
-          acc.x += lo;
-          acc.y += hi;
-          unpack2s<BF16>(r2.y, lo, hi);
-          acc.z += lo;
-          acc.w += hi;
+    // base address of every peer's tile in rank order (this CTA's own included)
+    uint32_t peer[8];
+#pragma unroll
+    for (uint32_t s = 0; s < 8; ++s)
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[s]) : "r"(tile_addr), "r"(s < S ? s : rank));
+    // One item = 4 columns of one row; thread t takes items t, t + 384, ... of the slice, walking
+    // (row, chunk) incrementally.  The step is instruction-bound, so the code per item is kept short:
+    // the first four peers' loads are issued together (clusters of up to 4 are the common case), the
+    // rest in a rolled loop; sums always run in rank order (bit-identical from run to run).
+    if (w4 > 0) {
+      int row = (int)threadIdx.x / w4, c = (int)threadIdx.x % w4;
+      const int step_r = kSkThreads / w4, step_c = kSkThreads % w4;
+      for (; row < M; row += step_r) {
+        const int n = n0 + (c_begin + c) * 4;
+        const uint32_t off = (uint32_t)(row * kSkBN + (c_begin + c) * 4) * 4u;
+        float4 acc = ld_dsmem_f4(peer[0] + off), v1, v2, v3;
+        if (S > 1) v1 = ld_dsmem_f4(peer[1] + off);
+        if (S > 2) v2 = ld_dsmem_f4(peer[2] + off);
+        if (S > 3) v3 = ld_dsmem_f4(peer[3] + off);
+        auto add = [&](const float4& v) {
+          acc.x += v.x;
+          acc.y += v.y;
+          acc.z += v.z;
+          acc.w += v.w;
+        };
+        if (S > 1) add(v1);
+        if (S > 2) add(v2);
+        if (S > 3) add(v3);
+#pragma unroll 1
+        for (uint32_t s = 4; s < S; ++s) add(ld_dsmem_f4(peer[s] + off));
+        if (n < N) {
+          if constexpr (EPI == 2) {
+            // columns n..n+3 are (gate, up), (gate, up) of outputs n/2 and n/2+1
+            *reinterpret_cast<uint32_t*>(C + (int64_t)row * ldc + n / 2) =
+                pack2s<BF16>(silu_mul_s(acc.x, acc.y), silu_mul_s(acc.z, acc.w));
+          } else {
+            if constexpr (EPI == 1) {
+              const uint2 r2 = *reinterpret_cast<const uint2*>(R + (int64_t)row * ldr + n);
+              float lo, hi;
+              unpack2s<BF16>(r2.x, lo, hi);
+              acc.x += lo;
+              acc.y += hi;
+              unpack2s<BF16>(r2.y, lo, hi);
+              acc.z += lo;
+              acc.w += hi;
+            }
+            uint2 o;
+            o.x = pack2s<BF16>(acc.x, acc.y);
+            o.y = pack2s<BF16>(acc.z, acc.w);
+            *reinterpret_cast<uint2*>(C + (int64_t)row * ldc + n) = o;
+          }
         }
-        uint2 o;
-        o.x = pack2s<BF16>(acc.x, acc.y);
-        o.y = pack2s<BF16>(acc.z, acc.w);
-        *reinterpret_cast<uint2*>(C + (int64_t)row * ldc + n) = o;
+        c += step_c;
+        if (c >= w4) {
+          c -= w4;
+          ++row;
+        }
       }
     }
   }
 
   // nobody leaves while a peer may still read its tile
-  cluster_sync_all();
+  if (S > 1) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc<1>(tmem_base, kTmemCols);
@@ -290,14 +350,29 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 
 }  // namespace
 
-// Cluster size (K-splits per column slab).  Measured on B200: the rate peaks near 96 CTAs in
-// flight (more splits add distributed-shared-memory reduction traffic faster than they add
-// bytes in flight), so S = round(96 / slabs), at most 8.  B200K_SKINNY_S overrides it.
-int skinny_cluster_size(int N, int K) {
-  const int tiles = (N + kSkBN - 1) / kSkBN;
+// Slab width and cluster size (K-splits per slab).  Measured on B200 (graph-replayed, M = 16..128):
+// 128-column slabs beat 256-column ones whenever they fit one wave (N = 4096: +20 %, 11008 x 4096:
+// +11..22 %; equal at N = 11008), because the partial tile a CTA has to drain and reduce is half as
+// large and fewer K-splits are needed for the same number of CTAs; beyond one wave of 128-column
+// slabs the 256-column slab is used.  The rate peaks with 96..128 CTAs (more splits add reduction work
+// faster than bytes in flight; more CTAs than SMs means a second wave), so S = round(112 / slabs),
+// at most 8, never more CTAs than SMs.  B200K_SKINNY_BN / B200K_SKINNY_S override both.
+int skinny_slab_width(int N) {
+  static const int env_bn = [] {
+    const char* e = getenv("B200K_SKINNY_BN");
+    return e ? atoi(e) : 0;
+  }();
+  if (env_bn == 128 || env_bn == 256) return env_bn;
+  const int sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
+  return (N + 127) / 128 <= sms ? 128 : 256;
+}
+int skinny_cluster_size(int N, int K, int bn) {
+  const int tiles = (N + bn - 1) / bn;
   const int num_kb = (K + kSkBK - 1) / kSkBK;
-  int s = (96 + tiles / 2) / tiles;
+  const int sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
+  int s = (112 + tiles / 2) / tiles;
   if (s > 8) s = 8;
+  while (s > 1 && s * tiles > sms) --s;
   if (s > num_kb / 2) s = num_kb / 2;
   if (s < 1) s = 1;
   if (const char* e = getenv("B200K_SKINNY_S")) {
@@ -307,11 +382,12 @@ int skinny_cluster_size(int N, int K) {
   return s;
 }
 
-template <int MPAD, bool BF16, int EPI>
+template <int MPAD, bool BF16, int EPI, int BN>
 static int launch_skinny_t(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
                            int64_t ldc, cudaStream_t stream, const void* R, int64_t ldr) {
-  using L = SkinnySmem<MPAD>;
-  auto kfn = gemm_skinny_kernel<MPAD, BF16, EPI>;
+  using L = SkinnySmem<MPAD, BN>;
+  constexpr int kSkBN = BN;
+  auto kfn = gemm_skinny_kernel<MPAD, BF16, EPI, BN>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -339,7 +415,7 @@ static int launch_skinny_t(const void* A, const void* B, void* C, int M, int N, 
   }
   int* status = status_ptr();
   if (!status) return B200K_ECUDA;
-  const int S = skinny_cluster_size(N, K);
+  const int S = skinny_cluster_size(N, K, kSkBN);
   const int tiles = (N + kSkBN - 1) / kSkBN;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(tiles * S));
@@ -366,9 +442,12 @@ static int launch_skinny_t(const void* A, const void* B, void* C, int M, int N, 
 int launch_skinny(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                   bool bf16, cudaStream_t stream, int epilogue, const void* R, int64_t ldr) {
   if (M > 128 || epilogue < 0 || epilogue > 2) return B200K_ESHAPE;
-#define B200K_SKINNY_E(MP, EP)                                                                         \
-  (bf16 ? launch_skinny_t<MP, true, EP>(A, B, C, M, N, K, lda, ldb, ldc, stream, R, ldr)                \
-        : launch_skinny_t<MP, false, EP>(A, B, C, M, N, K, lda, ldb, ldc, stream, R, ldr))
+  // tiny M on a wide weight: the epilogue is negligible and 512-byte rows stream a little better
+  const bool narrow = skinny_slab_width(N) == 128 && !(M <= 32 && (N + 127) / 128 > 64 && !getenv("B200K_SKINNY_BN"));
+#define B200K_SKINNY_B(MP, EP, BNN)                                                                      \
+  (bf16 ? launch_skinny_t<MP, true, EP, BNN>(A, B, C, M, N, K, lda, ldb, ldc, stream, R, ldr)            \
+        : launch_skinny_t<MP, false, EP, BNN>(A, B, C, M, N, K, lda, ldb, ldc, stream, R, ldr))
+#define B200K_SKINNY_E(MP, EP) (narrow ? B200K_SKINNY_B(MP, EP, 128) : B200K_SKINNY_B(MP, EP, 256))
 #define B200K_SKINNY(MP) \
   return epilogue == 0 ? B200K_SKINNY_E(MP, 0) : epilogue == 1 ? B200K_SKINNY_E(MP, 1) : B200K_SKINNY_E(MP, 2)
   if (M <= 16) { B200K_SKINNY(16); }
@@ -377,6 +456,7 @@ int launch_skinny(const void* A, const void* B, void* C, int M, int N, int K, in
   B200K_SKINNY(128);
 #undef B200K_SKINNY
 #undef B200K_SKINNY_E
+#undef B200K_SKINNY_B
 }
 
 }  // namespace b200k
