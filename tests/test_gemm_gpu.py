@@ -127,6 +127,30 @@ def test_skinny_split_k_clusters(cuda_device, shape, dtype):
     assert err <= TOL, err
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("splits", [1, 2, 5, 8])
+@pytest.mark.parametrize("shape", [(1, 136, 192), (7, 264, 200), (16, 512, 1024), (33, 1096, 520), (64, 2048, 512),
+                                   (100, 520, 264), (128, 384, 640)])
+def test_skinny_cluster_sizes_and_epilogues(cuda_device, monkeypatch, shape, splits, dtype):
+    """Every cluster size the heuristic can pick, forced through the documented override, with all
+    three epilogues: a cluster of one stores C straight from the accumulators (odd row counts, ragged
+    N), larger ones reduce through distributed shared memory (uneven column shares at 5 and 8)."""
+    from b200k import gemm
+    monkeypatch.setenv("B200K_SKINNY_S", str(splits))
+    M, N, K = shape
+    a, b = _inputs(M, N, K, dtype, seed=M + N + K + splits, std_b=0.1)
+    ad, bd = a.to(cuda_device), b.to(cuda_device)
+    ref = oracle.gemm_ref(a, b)
+    assert oracle.rel_frobenius(gemm.gemm(ad, bd, variant=3), ref) <= TOL
+    g = torch.Generator().manual_seed(5)
+    r = torch.randn(M, N, generator=g).to(dtype)
+    assert oracle.rel_frobenius(gemm.gemm_add(ad, bd, r.to(cuda_device)), ref + r.float()) <= TOL
+    if N % 16 == 0:
+        got = gemm.gemm_swiglu(ad, bd)
+        want = torch.nn.functional.silu(ref[:, 0::2]) * ref[:, 1::2]
+        assert got.shape == (M, N // 2) and oracle.rel_frobenius(got, want) <= TOL
+
+
 def test_skinny_rejects_large_m(cuda_device):
     from b200k import _lib, gemm
     a = torch.zeros(256, 64, dtype=torch.float16, device=cuda_device)

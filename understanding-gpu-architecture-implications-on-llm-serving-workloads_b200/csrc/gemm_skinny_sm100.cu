@@ -20,7 +20,7 @@
 //     to its own shared memory (the drained stage buffers), the cluster synchronises, and CTA r
 //     sums its share of the columns of all S tiles through distributed shared memory in rank
 //     order 0..S-1 (bit-identical from run to run), converts and stores its part of C.  A cluster
-//     of one needs no cluster barrier and none at exit.
+//     of one has final accumulators: its draining warps convert and store C themselves.
 //   * The same final step carries the fused epilogues of the wide kernels (EPI: 0 none, 1 residual
 //     add in fp32 before rounding, 2 SiLU(gate)*up over interleaved column pairs, output N/2 wide),
 //     so the o_proj / down_proj / gate-up projections of a decode step stream their weights the
@@ -90,6 +90,16 @@ __device__ __forceinline__ void unpack2s(uint32_t u, float& lo, float& hi) {
 // same formula as the wide kernels' SwiGLU epilogue
 __device__ __forceinline__ float silu_mul_s(float gate, float up) {
   return __fdividef(gate, 1.f + __expf(-gate)) * up;
+}
+template <bool BF16>
+__device__ __forceinline__ uint16_t pack1s(float x) {
+  if constexpr (BF16) {
+    const __nv_bfloat16 v = __float2bfloat16_rn(x);
+    return *reinterpret_cast<const uint16_t*>(&v);
+  } else {
+    const __half v = __float2half_rn(x);
+    return *reinterpret_cast<const uint16_t*>(&v);
+  }
 }
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2s(float lo, float hi) {
@@ -256,6 +266,34 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 #pragma unroll
           for (int e = 0; e < kChunk; ++e) v[e] = 0u;
         }
+        if (S == 1) {
+          // No split-K: the accumulators are final, so they go straight to C.  Lanes 2j and 2j+1 hold
+          // neighbouring columns of the same rows; they swap one value per pair of rows, after which
+          // the even lane owns both columns of row e and the odd lane both columns of row e+1.
+          const int col = (n0 + n) & ~1;
+          const bool odd = lane & 1;
+#pragma unroll
+          for (int e = 0; e < kChunk; e += 2) {
+            const uint32_t got = __shfl_xor_sync(0xffffffffu, odd ? v[e] : v[e + 1], 1);
+            const int m = cb * kChunk + e + (odd ? 1 : 0);
+            float lo = __uint_as_float(odd ? got : v[e]);
+            float hi = __uint_as_float(odd ? v[e + 1] : got);
+            if (m < M && col < N) {
+              if constexpr (EPI == 2) {
+                C[(int64_t)m * ldc + col / 2] = pack1s<BF16>(silu_mul_s(lo, hi));
+              } else {
+                if constexpr (EPI == 1) {
+                  float rl, rh;
+                  unpack2s<BF16>(*reinterpret_cast<const uint32_t*>(R + (int64_t)m * ldr + col), rl, rh);
+                  lo += rl;
+                  hi += rh;
+                }
+                *reinterpret_cast<uint32_t*>(C + (int64_t)m * ldc + col) = pack2s<BF16>(lo, hi);
+              }
+            }
+          }
+          continue;
+        }
 #pragma unroll
         for (int e = 0; e < kChunk; ++e) {
           const int m = cb * kChunk + e;
@@ -273,7 +311,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
   else
     cluster_sync_all();
 
-  {
+  if (S > 1) {
     // this CTA's slice of the tile's 16-byte chunks (any S in 1..8 divides them unevenly at most by one)
     const int c_begin = (int)rank * (kSkBN / 4) / (int)S;
     const int c_end = ((int)rank + 1) * (kSkBN / 4) / (int)S;
