@@ -393,8 +393,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 // +11..22 %; equal at N = 11008), because the partial tile a CTA has to drain and reduce is half as
 // large and fewer K-splits are needed for the same number of CTAs; beyond one wave of 128-column
 // slabs the 256-column slab is used.  The rate peaks with 96..128 CTAs (more splits add reduction work
-// faster than bytes in flight; more CTAs than SMs means a second wave), so S = round(112 / slabs),
-// at most 8, never more CTAs than SMs.  B200K_SKINNY_BN / B200K_SKINNY_S override both.
+// faster than bytes in flight; more CTAs than SMs means a second wave), so S = round(112 / slabs)
+// for 128-column slabs, round(96 / slabs) for 256-column ones, at most 8, never more CTAs than SMs.  B200K_SKINNY_BN / B200K_SKINNY_S override both.
 int skinny_slab_width(int N) {
   static const int env_bn = [] {
     const char* e = getenv("B200K_SKINNY_BN");
@@ -408,7 +408,8 @@ int skinny_cluster_size(int N, int K, int bn) {
   const int tiles = (N + bn - 1) / bn;
   const int num_kb = (K + kSkBK - 1) / kSkBK;
   const int sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
-  int s = (112 + tiles / 2) / tiles;
+  const int target = bn == 128 ? 112 : 96;  // CTAs in flight at which the measured rate peaks
+  int s = (target + tiles / 2) / tiles;
   if (s > 8) s = 8;
   while (s > 1 && s * tiles > sms) --s;
   if (s > num_kb / 2) s = num_kb / 2;
