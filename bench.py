@@ -260,6 +260,19 @@ def run_profile_case(args):
         ws = fmha.decode_workspace(B, Hq, Hkv, 1, Skv, D, 0, dev)
         fn = lambda: fmha.fmha_decode(q, k, v, kv_lens=lens, out=o, workspace=ws)
         work, unit = (float(lens.sum().item()) * Hkv * D * 4 + 2.0 * B * Hq * D * 2) / 1e9, "GB/s"
+    elif case == "skinny":
+        # the decode pairing: 64 rows against the 4096 x 11008 weight, four copies in rotation so that
+        # every launch streams its weight from HBM (one copy, 90 MB, would sit in the 126 MB L2)
+        Ms, Ks, Ns = 64, 4096, 11008
+        xs = inputs.device_randn16((Ms, Ks), 11, 1.0, torch.bfloat16, dev)
+        wts = [inputs.device_randn16((Ks, Ns), 20 + t, 0.02, torch.bfloat16, dev) for t in range(4)]
+        cs = torch.empty((Ms, Ns), dtype=torch.bfloat16, device=dev)
+        turn = [0]
+
+        def fn():
+            turn[0] = (turn[0] + 1) % len(wts)
+            gemm.gemm(xs, wts[turn[0]], out=cs)
+        work, unit = 2.0 * (Ks * Ns + Ms * Ks + Ms * Ns) / 1e9, "GB/s"
     else:
         raise SystemExit(f"unknown --profile-case {case}")
     secs = time_cuda(fn, n, max(1, args.warmup))
@@ -558,7 +571,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "fmha", "decode"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "fmha", "decode", "skinny"],
                     help="run only this path on a capture-sized case (for ncu); prints its own short line")
     ap.add_argument("--variant", type=int, default=0, help="GEMM kernel variant for --profile-case gemm")
     args = ap.parse_args()

@@ -540,10 +540,11 @@ extern "C" int b200k_gemm(const void* A, const void* B, void* C, int M, int N, i
       const int sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
       const long pair_tiles = (long)((M + 255) / 256) * ((N + 255) / 256);
       const long tiles256 = (long)((M + 127) / 128) * ((N + 255) / 256);
-      if (M <= 32 || (M <= 128 && (N + 127) / 128 < 64))
-        variant = B200K_GEMM_SKINNY;  // weight streaming, split-K inside clusters
-      else if (M <= 128)
-        variant = B200K_GEMM_1CTA_N128;  // wide weights: enough 128-column tiles without split-K
+      if (M <= 128)
+        // weight streaming (split-K inside clusters where the slabs alone do not fill the GPU): measured
+        // ahead of the 128-column tiles without split-K on every width from 4096 to 32000 columns for
+        // M <= 64 (up to +25 %), within -4 % .. +10 % of them for M = 100..128
+        variant = B200K_GEMM_SKINNY;
       else if (pair_tiles >= sms / 2)
         variant = B200K_GEMM_2CTA;  // at least one full wave of 256x256 pair tiles
       else
@@ -617,7 +618,7 @@ extern "C" int b200k_gemm_fused(const void* A, const void* B, void* C, const voi
   const bool big = pair_tiles >= sms / 2;
   const bool bf16 = dtype == B200K_BF16;
   // decode-shaped calls stream the weight like the plain skinny GEMM (same rule as b200k_gemm's AUTO)
-  if (M <= 32 || (M <= 128 && (N + 127) / 128 < 64))
+  if (M <= 128)
     return launch_skinny(A, B, C, M, N, K, lda, ldb, ldc, bf16, stream, epilogue, R, ldr);
 #define B200K_FUSED(EP)                                                                                       \
   (big ? (bf16 ? launch_tc<2, 256, 6, true, EP>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream, R, ldr)         \
