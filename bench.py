@@ -452,11 +452,29 @@ def run_ours(args):
         ssecs = max_over_ranks(time_cuda(skinny_step, ssteps, warmup, barrier, warm_seconds=0.03))
         sbytes = 2.0 * (Ks * Ns + Ms * Ks + Ms * Ns)
         sgbs = world * sbytes * ssteps / ssecs / 1e9
+        # the same launches replayed from a CUDA graph (as a serving loop would issue them): device time
+        # without the per-call host overhead of the Python binding
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(len(wts)):
+                skinny_step()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(len(wts)):
+                skinny_step()
+        gsteps = max(4, ssteps // len(wts))
+        gsecs = max_over_ranks(time_cuda(graph.replay, gsteps, 3, barrier)) / len(wts)
+        ggbs = world * sbytes * gsteps / gsecs / 1e9
         extra["skinny_gemm"] = {
-            "workload": "gemm_bf16_M64_K4096_N11008", "value": sgbs, "unit": "GB/s", "ms": ssecs / ssteps * 1e3,
-            "note": "one launch per call from Python; host launch overhead is inside this number",
-            "roofline": {"bound": "hbm", "achieved": sgbs / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": sgbs / world / peaks["hbm_gbs"], "traffic": None}}
+            "workload": "gemm_bf16_M64_K4096_N11008", "value": ggbs, "unit": "GB/s", "ms": gsecs / gsteps * 1e3,
+            "note": "launches replayed from a CUDA graph, weights rotated through 8 copies (HBM-resident, not L2)",
+            "per_call_from_python": {"value": sgbs, "unit": "GB/s", "ms": ssecs / ssteps * 1e3,
+                                     "note": "one launch per call through the ctypes binding, host overhead inside"},
+            "roofline": {"bound": "hbm", "achieved": ggbs / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": ggbs / world / peaks["hbm_gbs"], "traffic": 94146304}}
+        del graph
         del xs, wts, cs
     except Exception as exc:  # the headline number stands even if an extra fails
         extra["error"] = repr(exc)[:300]

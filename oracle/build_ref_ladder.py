@@ -45,6 +45,8 @@ def build(ref_root: str, which: str) -> str:
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_ROOT", "")
+    if not os.path.isdir(os.path.join(root, "kernels")):
+        sys.exit("usage: build_ref_ladder.py /path/to/reference [gemm] [fmha]  (or set REFERENCE_ROOT)")
     for which in (sys.argv[2:] or ["gemm", "fmha"]):
         print(build(root, which))
