@@ -42,7 +42,7 @@ namespace {
 constexpr int kFmhaThreads = 384;  // 2 softmax warpgroups + 1 warpgroup holding the TMA and MMA warps
 constexpr int kTile = 128;  // query rows per tile and keys per block
 constexpr float kRescaleThreshold = 8.0f;
-constexpr int kDefaultEmu = 1;
+constexpr int kDefaultEmu = 2;  // of every 8 score pairs, how many exponentials run on the FMA pipe
 // Register split by role (setmaxnreg).  setmaxnreg.inc waits until the CTA's pool - the registers it
 // was launched with: threads x the per-thread count ptxas chose under __launch_bounds__, a multiple
 // of 8 - has room, and waits for ever if the roles' claims add up to more than that pool, so every
@@ -57,7 +57,7 @@ static_assert(256 * kSoftmaxRegs + 128 * kAuxRegs <= kFmhaThreads * launch_regs(
 // P is handed to the MMA warp in kPParts pieces (1, 2 or 4) of 128 / kPParts keys, so that the PV
 // product of the first pieces runs while the softmax group still exponentiates the later ones.
 constexpr int kPParts = B200K_FMHA_P_PARTS;
-static_assert(kPParts == 1 || kPParts == 2 || kPParts == 4, "P is handed over in 1, 2 or 4 pieces");  // of every 4 score pairs, how many exponentials run on the FMA pipe
+static_assert(kPParts == 1 || kPParts == 2 || kPParts == 4, "P is handed over in 1, 2 or 4 pieces");
 
 template <int D>
 struct FmhaSmem {
@@ -222,13 +222,13 @@ __device__ __forceinline__ void softmax_block(uint32_t s_tmem, uint32_t o_tmem, 
     const uint64_t sc2 = f2pack(sc, sc), neg2 = f2pack(neg, neg);
 #pragma unroll
     for (int e = 0; e < 16; e += 4) {
-      // 8 scores = 4 pairs per step; the last EMU pairs go to the FMA pipe, the rest to the MUFU
+      // of every 8 score pairs the last EMU take their exponentials on the FMA pipe, the rest on the MUFU
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         const int k = qt * 32 + (e + g) * 2;
         const uint64_t x2 = fma2(f2pack(__uint_as_float(s[k]), __uint_as_float(s[k + 1])), sc2, neg2);
         float p0, p1;
-        if (g >= 4 - EMU) {
+        if (((e + g) & 7) >= 8 - EMU) {
           ex2_emulated(x2, p0, p1);
         } else {
           float x0, x1;
@@ -274,7 +274,7 @@ __device__ __forceinline__ void softmax_block(uint32_t s_tmem, uint32_t o_tmem, 
 }
 
 
-// EMU: how many of every 4 score pairs take their exponentials on the FMA pipe (0, 1 or 2).
+// EMU: how many of every 8 score pairs take their exponentials on the FMA pipe (0..4).
 template <int D, bool BF16, int EMU>
 __global__ void __launch_bounds__(kFmhaThreads, 1)
 fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -1060,9 +1060,9 @@ extern "C" int b200k_fmha_fwd(const void* Q, const void* K, const void* V, void*
     return B200K_EALIGN;
   if (!b200k_device_supported()) return B200K_ENOGPU;
   const bool bf16 = dtype == B200K_BF16;
-  // variant: 0 = default; 1, 2, 3 = 0, 1, 2 of every 4 score pairs take their exponential on the
-  // FMA pipe instead of the MUFU (kept selectable for ablation)
-  // 11, 12, 13 = the same three with the persistent kernel
+  // variant: 0 = default; 1, 2, 3, 4, 5 = 0, 2, 4, 1, 3 of every 8 score pairs take their exponential
+  // on the FMA pipe instead of the MUFU (kept selectable for ablation)
+  // 11 .. 15 = the same five with the persistent kernel
   // Default: the persistent kernel for kv_len <= 4096 (measured +3 % at 4096, +10 % at 2048, +19..31 %
   // at 1024, where per-CTA set-up weighs most), the one-item-per-CTA kernel beyond (measured 5-7 %
   // ahead at 8192 / 16384, where the hardware's dynamic CTA scheduling balances better than the static
@@ -1072,12 +1072,16 @@ extern "C" int b200k_fmha_fwd(const void* Q, const void* K, const void* V, void*
     return e ? (e[0] == '1' ? 1 : 0) : -1;
   }();
   const bool persistent = variant != 0 ? variant >= 10 : env_persistent >= 0 ? env_persistent == 1 : kv_len <= 4096;
-  const int emu = variant == 0 ? kDefaultEmu : (variant % 10) - 1;
-  if (emu < 0 || emu > 2) return B200K_EARG;
+  static const int kEmuOfCode[5] = {0, 2, 4, 1, 3};
+  const int code = (variant % 10) - 1;
+  if (variant != 0 && (code < 0 || code > 4 || variant >= 20)) return B200K_EARG;
+  const int emu = variant == 0 ? kDefaultEmu : kEmuOfCode[code];
 #define B200K_FMHA(DD, BF, EM)                                                                                  \
   launch_fmha<DD, BF, EM>(Q, K, V, O, B, Hq, Hkv, Sq, kv_len, q_strides, k_strides, v_strides, o_strides, scale, \
                           causal, persistent, stream)
-#define B200K_FMHA_EMU(DD, BF) (emu == 0 ? B200K_FMHA(DD, BF, 0) : emu == 1 ? B200K_FMHA(DD, BF, 1) : B200K_FMHA(DD, BF, 2))
+#define B200K_FMHA_EMU(DD, BF)                                                                  \
+  (emu == 0 ? B200K_FMHA(DD, BF, 0) : emu == 1 ? B200K_FMHA(DD, BF, 1) : emu == 2 ? B200K_FMHA(DD, BF, 2) \
+   : emu == 3 ? B200K_FMHA(DD, BF, 3) : B200K_FMHA(DD, BF, 4))
   if (D == 128) return bf16 ? B200K_FMHA_EMU(128, true) : B200K_FMHA_EMU(128, false);
   return bf16 ? B200K_FMHA_EMU(64, true) : B200K_FMHA_EMU(64, false);
 #undef B200K_FMHA_EMU
