@@ -59,16 +59,44 @@ static_assert(256 * kSoftmaxRegs + 128 * kAuxRegs <= kFmhaThreads * launch_regs(
 constexpr int kPParts = B200K_FMHA_P_PARTS;
 static_assert(kPParts == 1 || kPParts == 2 || kPParts == 4, "P is handed over in 1, 2 or 4 pieces");
 
+// Row sums on the tensor pipe (head dimension 64 only, where TMEM has 128 spare columns): every V
+// stage is followed by a 64-wide box filled with ones, the PV product runs with N = D + 16, and the 16
+// extra accumulator columns of a row all hold sum_k P[row][k] - the softmax denominator, summed from the
+// same rounded P that multiplies V and rescaled together with O.  The softmax threads then issue no
+// additions for it (a score costs about 6 issue cycles; the sum was one of them).
+// Used by the one-item-per-CTA kernel (measured +4 % at d = 64, +10 % together with 3 of 8 exponentials
+// emulated); the persistent kernel, whose items are short, measured 1-6 % slower with it (the PV
+// product is a quarter longer) and keeps the sums in registers.
+template <int D, bool PERSISTENT>
+constexpr bool kSumOnTensor = D == 64 && !PERSISTENT;
+template <int D, bool PERSISTENT>
+constexpr uint32_t kOCols = D + (kSumOnTensor<D, PERSISTENT> ? 16 : 0);  // accumulator columns of one tile
+
 template <int D>
 struct FmhaSmem {
   static constexpr uint32_t kTileBytes = kTile * D * 2;  // one Q tile, K block or V block
   static constexpr uint32_t kHalfBytes = kTile * 128;    // one 64-wide (128-byte) column box
+  static constexpr uint32_t kVStride = kTileBytes + (kSumOnTensor<D, false> ? kHalfBytes : 0);  // V stage (+ ones box)
   static constexpr uint32_t kQOff = 0;
   static constexpr uint32_t kKOff = 2 * kTileBytes;
   static constexpr uint32_t kVOff = 4 * kTileBytes;
-  static constexpr uint32_t kBarOff = 6 * kTileBytes;
+  static constexpr uint32_t kBarOff = kVOff + 2 * kVStride;
   static constexpr uint32_t kTotal = kBarOff + 256 + 1024;
 };
+
+// fills the ones boxes behind both V stages (all threads of the CTA, before the roles split)
+template <int D, bool BF16, bool PERSISTENT, typename L>
+__device__ __forceinline__ void fill_ones_boxes(uint8_t* smem) {
+  if constexpr (kSumOnTensor<D, PERSISTENT>) {
+    const uint32_t one2 = BF16 ? 0x3f803f80u : 0x3c003c00u;
+    const uint4 w = make_uint4(one2, one2, one2, one2);
+    for (int s = 0; s < 2; ++s) {
+      uint4* box = reinterpret_cast<uint4*>(smem + L::kVOff + s * L::kVStride + L::kTileBytes);
+      for (uint32_t t = threadIdx.x; t < L::kHalfBytes / 16; t += blockDim.x) box[t] = w;
+    }
+    fence_proxy_async_smem();  // read by the tensor core through the async proxy
+  }
+}
 
 struct FmhaParams {
   int B, Hq, Hkv, Sq;
@@ -168,7 +196,7 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
 // row of the warp, so P may reach 2^threshold.
 //   lim: local index of the last visible key of this row in this block (masked = some row of the tile
 //   has lim < 127); s_tmem / o_tmem: this thread's lane of the S and O accumulators.
-template <int D, bool BF16, int EMU>
+template <int D, bool BF16, int EMU, bool SUMTC>
 __device__ __forceinline__ void softmax_block(uint32_t s_tmem, uint32_t o_tmem, bool first, bool masked, int lim,
                                               float sc, float& m_use, float& l, uint64_t* p_part_i,
                                               uint64_t* p_ready_i) {
@@ -215,6 +243,15 @@ __device__ __forceinline__ void softmax_block(uint32_t s_tmem, uint32_t o_tmem, 
       }
       tmem_st32(o_tmem + c * 32, o);
     }
+    if constexpr (SUMTC) {
+      // the row-sum columns behind O
+      uint32_t o[16];
+      tmem_ld16(o_tmem + D, o);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
+      tmem_st16(o_tmem + D, o);
+    }
   };
   // a quarter of the block: 32 keys -> 16 packed columns
   auto quarter = [&](int qt, uint32_t (&pk)[16], uint64_t& sum_a, uint64_t& sum_b) {
@@ -236,10 +273,12 @@ __device__ __forceinline__ void softmax_block(uint32_t s_tmem, uint32_t o_tmem, 
           p0 = ex2(x0);
           p1 = ex2(x1);
         }
-        if (g & 1)
-          sum_b = add2(sum_b, f2pack(p0, p1));
-        else
-          sum_a = add2(sum_a, f2pack(p0, p1));
+        if constexpr (!SUMTC) {
+          if (g & 1)
+            sum_b = add2(sum_b, f2pack(p0, p1));
+          else
+            sum_a = add2(sum_a, f2pack(p0, p1));
+        }
         pk[e + g] = pack16<BF16>(p0, p1);
       }
     }
@@ -268,9 +307,11 @@ __device__ __forceinline__ void softmax_block(uint32_t s_tmem, uint32_t o_tmem, 
   tmem_st_wait();
   tc_fence_before();
   mbar_arrive(p_ready_i);
-  float a, b;
-  f2unpack(add2(sum_a, sum_b), a, b);
-  l += a + b;
+  if constexpr (!SUMTC) {
+    float a, b;
+    f2unpack(add2(sum_a, sum_b), a, b);
+    l += a + b;
+  }
 }
 
 
@@ -283,7 +324,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   using L = FmhaSmem<D>;
   constexpr int kDBoxes = D / 64;  // 64-wide column boxes per row
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kSCol0 = 0, kSCol1 = 128, kOCol0 = 256, kOCol1 = 256 + D;
+  constexpr uint32_t kSCol0 = 0, kSCol1 = 128, kOCol0 = 256, kOCol1 = 256 + kOCols<D, false>;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -359,6 +400,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tmem_alloc<1>(tmem_holder, kTmemCols);
     tmem_relinquish<1>();
   }
+  fill_ones_boxes<D, BF16, false, L>(smem);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -387,7 +429,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           report_timeout(p.status, KID_FMHA, ROLE_PRODUCER);
           break;
         }
-        load_tile(&tmV, smem + L::kVOff + s * L::kTileBytes, &v_full[s], j * kTile, hk);
+        load_tile(&tmV, smem + L::kVOff + s * L::kVStride, &v_full[s], j * kTile, hk);
         if (j + 1 < nb_max) {
           const int s1 = (j + 1) & 1;
           const uint32_t ph1 = ((j + 1) >> 1) & 1;
@@ -404,7 +446,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     reg_dealloc<kAuxRegs>();
     if (elect_one() && nb_max > 0) {
       constexpr uint32_t idesc_s = make_idesc_f16(BF16 ? 1 : 0, 0, 0, kTile, kTile);
-      constexpr uint32_t idesc_pv = make_idesc_f16(BF16 ? 1 : 0, 0, 1, kTile, D);
+      constexpr uint32_t idesc_pv = make_idesc_f16(BF16 ? 1 : 0, 0, 1, kTile, kOCols<D, false>);
       const uint32_t q_addr = smem_u32(smem + L::kQOff);
       const uint32_t k_addr = smem_u32(smem + L::kKOff);
       const uint32_t v_addr = smem_u32(smem + L::kVOff);
@@ -431,7 +473,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // O_i += P_i . V_stage : 8 steps of 16 keys; P from TMEM (8 columns of 16-bit pairs per
       // step), V MN-major: 16 keys = 16 rows of 128 bytes; 64-wide d boxes kHalfBytes apart.
       auto issue_pv = [&](int i, int stage, bool first, int kk0, int kk1) {
-        const uint32_t va = v_addr + stage * L::kTileBytes;
+        const uint32_t va = v_addr + stage * L::kVStride;
 #pragma unroll
         for (int kk = kk0; kk < kk1; ++kk) {
           umma_ts(tmem_base + o_col[i], tmem_base + s_col[i] + kk * 8,
@@ -521,7 +563,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tc_fence_after();
         const int k0 = j * kTile;
-        softmax_block<D, BF16, EMU>(s_tmem, o_tmem, j == 0, k0 + kTile - 1 > tile_min_lim, lim_row - k0, sc, m_use, l,
+        softmax_block<D, BF16, EMU, kSumOnTensor<D, false>>(s_tmem, o_tmem, j == 0, k0 + kTile - 1 > tile_min_lim, lim_row - k0, sc, m_use, l,
                                     &p_part[i], &p_ready[i]);
       }
 
@@ -534,6 +576,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_after();
       }
       if (ok) {
+        if constexpr (kSumOnTensor<D, false>) {
+          if (nb[i] > 0) {  // the denominator was summed by the PV products: 16 equal columns behind O
+            const uint32_t t = tmem_ld1(o_tmem + D);
+            tmem_ld_wait();
+            l = __uint_as_float(t);
+          }
+        }
         const float inv = l > 0.f ? 1.f / l : 0.f;
         uint8_t* stage = smem + L::kQOff + i * L::kTileBytes;  // Q_i is no longer read
 #pragma unroll
@@ -598,8 +647,9 @@ struct FmhaPSmem {
   static constexpr uint32_t kHalfBytes = kTile * 128;
   static constexpr uint32_t kQOff = 0;
   static constexpr uint32_t kKOff = 2 * kTileBytes;
+  static constexpr uint32_t kVStride = kTileBytes + (kSumOnTensor<D, true> ? kHalfBytes : 0);  // V stage (+ ones box)
   static constexpr uint32_t kVOff = 4 * kTileBytes;
-  static constexpr uint32_t kStageOff = 6 * kTileBytes;        // 2 x 16 KB output staging
+  static constexpr uint32_t kStageOff = kVOff + 2 * kVStride;  // 2 x 16 KB output staging
   static constexpr uint32_t kBarOff = kStageOff + 2 * kHalfBytes;
   static constexpr uint32_t kTotal = kBarOff + 256 + 1024;
 };
@@ -650,7 +700,7 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
   using L = FmhaPSmem<D>;
   constexpr int kDBoxes = D / 64;
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kSCol0 = 0, kSCol1 = 128, kOCol0 = 256, kOCol1 = 256 + D;
+  constexpr uint32_t kSCol0 = 0, kSCol1 = 128, kOCol0 = 256, kOCol1 = 256 + kOCols<D, true>;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -701,6 +751,7 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     tmem_alloc<1>(tmem_holder, kTmemCols);
     tmem_relinquish<1>();
   }
+  fill_ones_boxes<D, BF16, true, L>(smem);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -752,7 +803,7 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
             ok = false;
             break;
           }
-          load_tile(&tmV, smem + L::kVOff + st * L::kTileBytes, &v_full[st], j * kTile, it.hk, it.b);
+          load_tile(&tmV, smem + L::kVOff + st * L::kVStride, &v_full[st], j * kTile, it.hk, it.b);
           ++vc;
           if (j + 1 < it.nb_max) load_k(it, j + 1);
         }
@@ -763,7 +814,7 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     reg_dealloc<kPersistAuxRegs>();
     if (elect_one()) {
       constexpr uint32_t idesc_s = make_idesc_f16(BF16 ? 1 : 0, 0, 0, kTile, kTile);
-      constexpr uint32_t idesc_pv = make_idesc_f16(BF16 ? 1 : 0, 0, 1, kTile, D);
+      constexpr uint32_t idesc_pv = make_idesc_f16(BF16 ? 1 : 0, 0, 1, kTile, kOCols<D, true>);
       const uint32_t q_addr = smem_u32(smem + L::kQOff);
       const uint32_t k_addr = smem_u32(smem + L::kKOff);
       const uint32_t v_addr = smem_u32(smem + L::kVOff);
@@ -787,7 +838,7 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         umma_commit<1>(&s_full[i]);
       };
       auto issue_pv = [&](int i, uint32_t stage, bool first, int kk0, int kk1) {
-        const uint32_t va = v_addr + stage * L::kTileBytes;
+        const uint32_t va = v_addr + stage * L::kVStride;
 #pragma unroll
         for (int kk = kk0; kk < kk1; ++kk) {
           umma_ts(tmem_base + o_col[i], tmem_base + s_col[i] + kk * 8,
@@ -906,7 +957,7 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         ++sn;
         tc_fence_after();
         const int k0 = j * kTile;
-        softmax_block<D, BF16, EMU>(s_tmem, o_tmem, j == 0, k0 + kTile - 1 > tile_min_lim, lim_row - k0, sc, m_use, l,
+        softmax_block<D, BF16, EMU, kSumOnTensor<D, true>>(s_tmem, o_tmem, j == 0, k0 + kTile - 1 > tile_min_lim, lim_row - k0, sc, m_use, l,
                                     &p_part[i], &p_ready[i]);
       }
       if (!ok) break;
@@ -921,6 +972,11 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         }
         ++itn;
         tc_fence_after();
+        if constexpr (kSumOnTensor<D, true>) {  // the denominator was summed by the PV products
+          const uint32_t t = tmem_ld1(o_tmem + D);
+          tmem_ld_wait();
+          l = __uint_as_float(t);
+        }
       }
       const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
@@ -1075,7 +1131,8 @@ extern "C" int b200k_fmha_fwd(const void* Q, const void* K, const void* V, void*
   static const int kEmuOfCode[5] = {0, 2, 4, 1, 3};
   const int code = (variant % 10) - 1;
   if (variant != 0 && (code < 0 || code > 4 || variant >= 20)) return B200K_EARG;
-  const int emu = variant == 0 ? kDefaultEmu : kEmuOfCode[code];
+  // measured best: 2 of 8 emulated, except the one-item kernel at d = 64 (row sums on the tensor pipe), 3 of 8
+  const int emu = variant != 0 ? kEmuOfCode[code] : (D == 64 && !persistent) ? 3 : kDefaultEmu;
 #define B200K_FMHA(DD, BF, EM)                                                                                  \
   launch_fmha<DD, BF, EM>(Q, K, V, O, B, Hq, Hkv, Sq, kv_len, q_strides, k_strides, v_strides, o_strides, scale, \
                           causal, persistent, stream)
