@@ -16,11 +16,16 @@
 //     128 weight columns and k-step, accumulators D[weight column][activation row] in TMEM); eight
 //     warps that drain; two more that only help in the final step.  Draining and reducing are
 //     instruction-bound (the streaming loop itself runs at the HBM rate), hence the many warps.
-//   * The split-K partials never go to HBM: every CTA writes its fp32 partial tile [row][slab]
-//     to its own shared memory (the drained stage buffers), the cluster synchronises, and CTA r
-//     sums its share of the columns of all S tiles through distributed shared memory in rank
-//     order 0..S-1 (bit-identical from run to run), converts and stores its part of C.  A cluster
-//     of one has final accumulators: its draining warps convert and store C themselves.
+//   * The split-K partials never go to HBM.  CTA r of a cluster owns a share of the slab's columns.
+//     Narrow slabs: every CTA pushes its fp32 partials of a column straight from the accumulators into
+//     the owner's receive buffer (remote shared-memory stores, one slot per source CTA), ONE cluster
+//     barrier, then every owner sums its S slots locally in rank order 0..S-1 (bit-identical from run
+//     to run), converts and stores its part of C; nothing remote is touched after the barrier, so
+//     nobody waits at exit.  Wide slabs and 128 activation rows (no room for a receive buffer next to
+//     the stage ring): every
+//     CTA writes its partial tile to its own drained stage buffers, cluster barrier, owners pull their
+//     columns from all S tiles through distributed shared memory, second barrier before exit.  A
+//     cluster of one has final accumulators: its draining warps convert and store C themselves.
 //   * The same final step carries the fused epilogues of the wide kernels (EPI: 0 none, 1 residual
 //     add in fp32 before rounding, 2 SiLU(gate)*up over interleaved column pairs, output N/2 wide),
 //     so the o_proj / down_proj / gate-up projections of a decode step stream their weights the
@@ -54,11 +59,19 @@ struct SkinnySmem {
   static constexpr uint32_t kSkWBytes = BN * kSkBK * 2;
   static constexpr uint32_t kXBytes = MPAD * kSkBK * 2;  // activation tile of one stage
   static constexpr uint32_t kStageBytes = kSkWBytes + (kXBytes < 1024 ? 1024 : kXBytes);
-  // one CTA per SM: as many stages as fit in ~208 KB, at most 6 (8 with the narrow slab)
+  // Split-K reduction of the narrow slab: partials are PUSHED into the owner's receive buffer (one slot
+  // per source CTA, MPAD rows of at most BN/S + 3 columns), which must not alias the stage buffers
+  // because peers push while this CTA may still be streaming.  The wide slab keeps the pull scheme over
+  // a tile that reuses the drained stage buffers.
+  static constexpr bool kPush = BN == 128 && MPAD <= 64;  // at 128 rows the buffer would cost two of six stages (measured -5..-17 %)
+  static constexpr uint32_t kRecvBytes = kPush ? MPAD * (BN + 32) * 4 : 0;
+  // one CTA per SM: as many stages as fit in ~208 KB next to the receive buffer, at most 6 (8 narrow)
   static constexpr int kMaxStages = BN == 256 ? 6 : 8;
-  static constexpr int kStages = (208 * 1024 / kStageBytes) > kMaxStages ? kMaxStages : (208 * 1024 / kStageBytes);
-  static constexpr uint32_t kTileBytes = MPAD * kSkBN * 4;  // fp32 partial tile, reuses the stage buffers
-  static constexpr uint32_t kBarOff = kStages * kStageBytes > kTileBytes ? kStages * kStageBytes : kTileBytes;
+  static constexpr int kFit = (208 * 1024 - kRecvBytes) / kStageBytes;
+  static constexpr int kStages = kFit > kMaxStages ? kMaxStages : kFit;
+  static constexpr uint32_t kTileBytes = kPush ? 0 : MPAD * kSkBN * 4;  // fp32 partial tile, reuses the stage buffers
+  static constexpr uint32_t kRecvOff = kStages * kStageBytes > kTileBytes ? kStages * kStageBytes : kTileBytes;
+  static constexpr uint32_t kBarOff = kRecvOff + kRecvBytes;
   static constexpr uint32_t kTotal = kBarOff + 256 + 1024;  // barriers (2 per stage + 1) and the TMEM address, alignment slack
 };
 
@@ -266,6 +279,26 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 #pragma unroll
           for (int e = 0; e < kChunk; ++e) v[e] = 0u;
         }
+        if (L::kPush && S > 1) {
+          // Push this CTA's partial of column n into slot `rank` of the receive buffer of the CTA that
+          // owns the column's 16-byte chunk: consecutive lanes, consecutive words (plain remote stores).
+          const int c = n >> 2;                                          // chunk of 4 columns, 0..31
+          const int owner = ((c + 1) * (int)S - 1) / (kSkBN / 4);        // r with c_begin(r) <= c < c_end(r)
+          const int c_first = owner * (kSkBN / 4) / (int)S;              // first chunk of the owner's slice
+          const int wmax = 4 * ((kSkBN / 4 + (int)S - 1) / (int)S);      // floats per row of a slot
+          uint32_t base;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                       : "=r"(base)
+                       : "r"(smem_u32(smem + L::kRecvOff)), "r"((uint32_t)owner));
+          base += (uint32_t)(((int)rank * MPAD * wmax + (n - 4 * c_first)) * 4);
+#pragma unroll
+          for (int e = 0; e < kChunk; ++e) {
+            const int m = cb * kChunk + e;
+            if (m < M)
+              asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(base + (uint32_t)(m * wmax * 4)), "r"(v[e]) : "memory");
+          }
+          continue;
+        }
         if (S == 1) {
           // No split-K: the accumulators are final, so they go straight to C.  Lanes 2j and 2j+1 hold
           // neighbouring columns of the same rows; they swap one value per pair of rows, after which
@@ -332,10 +365,21 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       for (; row < M; row += step_r) {
         const int n = n0 + (c_begin + c) * 4;
         const uint32_t off = (uint32_t)(row * kSkBN + (c_begin + c) * 4) * 4u;
-        float4 acc = ld_dsmem_f4(peer[0] + off), v1, v2, v3;
-        if (S > 1) v1 = ld_dsmem_f4(peer[1] + off);
-        if (S > 2) v2 = ld_dsmem_f4(peer[2] + off);
-        if (S > 3) v3 = ld_dsmem_f4(peer[3] + off);
+        // partial of source CTA s: pushed into this CTA's receive buffer (narrow slab), or read from the
+        // source's own tile through distributed shared memory (wide slab)
+        auto part = [&](uint32_t s) -> float4 {
+          if constexpr (L::kPush) {
+            const int wmax = 4 * ((kSkBN / 4 + (int)S - 1) / (int)S);
+            return *reinterpret_cast<const float4*>(smem + L::kRecvOff +
+                                                    (((int)s * MPAD + row) * wmax + c * 4) * 4);
+          } else {
+            return ld_dsmem_f4(peer[s] + off);
+          }
+        };
+        float4 acc = part(0), v1, v2, v3;
+        if (S > 1) v1 = part(1);
+        if (S > 2) v2 = part(2);
+        if (S > 3) v3 = part(3);
         auto add = [&](const float4& v) {
           acc.x += v.x;
           acc.y += v.y;
@@ -346,7 +390,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         if (S > 2) add(v2);
         if (S > 3) add(v3);
 #pragma unroll 1
-        for (uint32_t s = 4; s < S; ++s) add(ld_dsmem_f4(peer[s] + off));
+        for (uint32_t s = 4; s < S; ++s) add(part(s));
         if (n < N) {
           if constexpr (EPI == 2) {
             // columns n..n+3 are (gate, up), (gate, up) of outputs n/2 and n/2+1
@@ -378,8 +422,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     }
   }
 
-  // nobody leaves while a peer may still read its tile
-  if (S > 1) cluster_sync_all();
+  // pull scheme: nobody leaves while a peer may still read its tile (after the push scheme's single
+  // barrier nobody touches another CTA's memory any more)
+  if (S > 1 && !L::kPush) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc<1>(tmem_base, kTmemCols);
