@@ -57,3 +57,29 @@ def test_decode_random_lengths(cuda_device, b, hkv, group, skv, d, splits, data)
                          num_splits=splits)
     ref = oracle.fmha_ref(q, k, v, kv_lens=lens)
     assert oracle.max_abs(o, ref) <= oracle.FMHA_MAX_ABS_TOL, (lens.tolist(), skv, d, splits)
+
+
+@settings(**dict(_SETTINGS, max_examples=40))
+@given(m=st.integers(1, 128), n16=st.sampled_from([1, 2, 5, 8, 9, 17, 40, 64, 129, 344, 600, 768]), k8=st.integers(1, 300),
+       bf16=st.booleans(), epilogue=st.sampled_from(["none", "add", "swiglu"]))
+def test_skinny_random_shapes_and_epilogues(cuda_device, m, n16, k8, bf16, epilogue):
+    """Decode-shaped GEMMs (M <= 128) over narrow to very wide weights: every combination of slab width
+    (128 / 256 columns), cluster size (1 = direct store, push and pull reductions) and epilogue that the
+    heuristics can pick must match the oracle."""
+    from b200k import gemm
+    N, K = n16 * 16, k8 * 8
+    dtype = torch.bfloat16 if bf16 else torch.float16
+    g = torch.Generator().manual_seed(m * 1000003 + N * 1009 + K)
+    a = torch.randn(m, K, generator=g).to(dtype)
+    b = (torch.randn(K, N, generator=g) * 0.1).to(dtype)
+    ref = oracle.gemm_ref(a, b)
+    ad, bd = a.to(cuda_device), b.to(cuda_device)
+    if epilogue == "none":
+        got, want = gemm.gemm(ad, bd), ref
+    elif epilogue == "add":
+        r = torch.randn(m, N, generator=g).to(dtype)
+        got, want = gemm.gemm_add(ad, bd, r.to(cuda_device)), ref + r.float()
+    else:
+        got, want = gemm.gemm_swiglu(ad, bd), torch.nn.functional.silu(ref[:, 0::2]) * ref[:, 1::2]
+    err = oracle.rel_frobenius(got, want)
+    assert err <= oracle.GEMM_REL_FRO_TOL, (m, N, K, dtype, epilogue, err)
