@@ -17,12 +17,12 @@
 //     warps that drain; two more that only help in the final step.  Draining and reducing are
 //     instruction-bound (the streaming loop itself runs at the HBM rate), hence the many warps.
 //   * The split-K partials never go to HBM.  CTA r of a cluster owns a share of the slab's columns.
-//     Narrow slabs: every CTA pushes its fp32 partials of a column straight from the accumulators into
+//     Push scheme: every CTA pushes its fp32 partials of a column straight from the accumulators into
 //     the owner's receive buffer (remote shared-memory stores, one slot per source CTA), ONE cluster
 //     barrier, then every owner sums its S slots locally in rank order 0..S-1 (bit-identical from run
 //     to run), converts and stores its part of C; nothing remote is touched after the barrier, so
-//     nobody waits at exit.  Wide slabs and 128 activation rows (no room for a receive buffer next to
-//     the stage ring): every
+//     nobody waits at exit.  Where the buffer would cost a stage of the ring that matters more (wide
+//     slabs above 16 rows, 128 activation rows): every
 //     CTA writes its partial tile to its own drained stage buffers, cluster barrier, owners pull their
 //     columns from all S tiles through distributed shared memory, second barrier before exit.  A
 //     cluster of one has final accumulators: its draining warps convert and store C themselves.
@@ -59,11 +59,12 @@ struct SkinnySmem {
   static constexpr uint32_t kSkWBytes = BN * kSkBK * 2;
   static constexpr uint32_t kXBytes = MPAD * kSkBK * 2;  // activation tile of one stage
   static constexpr uint32_t kStageBytes = kSkWBytes + (kXBytes < 1024 ? 1024 : kXBytes);
-  // Split-K reduction of the narrow slab: partials are PUSHED into the owner's receive buffer (one slot
-  // per source CTA, MPAD rows of at most BN/S + 3 columns), which must not alias the stage buffers
-  // because peers push while this CTA may still be streaming.  The wide slab keeps the pull scheme over
-  // a tile that reuses the drained stage buffers.
-  static constexpr bool kPush = BN == 128 && MPAD <= 64;  // at 128 rows the buffer would cost two of six stages (measured -5..-17 %)
+  // Split-K reduction, push scheme: partials go straight into the owner's receive buffer (one slot per
+  // source CTA, MPAD rows of at most BN/S + 3 columns), which must not alias the stage buffers because
+  // peers push while this CTA may still be streaming, so it costs ring stages.  Measured against the pull
+  // scheme (a tile that reuses the drained stage buffers): narrow slab up to 64 rows +8..10 %, wide slab
+  // at 16 rows +3..5 %; wide slab at 32 rows -5 % (the fifth stage goes), 128 rows -5..-17 % (two of six).
+  static constexpr bool kPush = (BN == 128 && MPAD <= 64) || (BN == 256 && MPAD <= 16);
   static constexpr uint32_t kRecvBytes = kPush ? MPAD * (BN + 32) * 4 : 0;
   // one CTA per SM: as many stages as fit in ~208 KB next to the receive buffer, at most 6 (8 narrow)
   static constexpr int kMaxStages = BN == 256 ? 6 : 8;
