@@ -56,11 +56,11 @@ def fmha_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = F
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     L = _lib.lib()
-    with torch.cuda.device(q.device):
+    with _lib.on_device(q.device):
         code = L.b200k_fmha_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, Hq, Hkv, Sq, Skv, D,
                                 _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(out),
                                 float(scale), int(bool(causal)), int(min(kv_len, Skv)), _DTYPES[q.dtype], int(variant),
-                                torch.cuda.current_stream(q.device).cuda_stream)
+                                _lib.raw_stream(q.device))
     _lib.check(code, "b200k_fmha_fwd")
     return out
 
@@ -100,13 +100,13 @@ def fmha_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_lens: torc
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     L = _lib.lib()
-    with torch.cuda.device(q.device):
+    with _lib.on_device(q.device):
         if static_scratch:
             code = L.b200k_fmha_decode_splitkv_static(
                 q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, Hq, Hkv, Sq, Skv, D,
                 _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(out), float(scale),
                 kv_lens.data_ptr() if kv_lens is not None else None, int(num_splits), _DTYPES[q.dtype],
-                torch.cuda.current_stream(q.device).cuda_stream)
+                _lib.raw_stream(q.device))
             _lib.check(code, "b200k_fmha_decode_splitkv_static")
             return out
         if workspace is None:
@@ -115,7 +115,7 @@ def fmha_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_lens: torc
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, Hq, Hkv, Sq, Skv, D,
             _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(out), float(scale),
             kv_lens.data_ptr() if kv_lens is not None else None, int(num_splits), _DTYPES[q.dtype],
-            workspace.data_ptr(), workspace.numel(), torch.cuda.current_stream(q.device).cuda_stream)
+            workspace.data_ptr(), workspace.numel(), _lib.raw_stream(q.device))
     _lib.check(code, "b200k_fmha_decode_splitkv")
     return out
 
@@ -145,12 +145,12 @@ def fmha_decode_paged(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     L = _lib.lib()
-    with torch.cuda.device(q.device):
+    with _lib.on_device(q.device):
         ws = decode_workspace(B, Hq, Hkv, Sq, max_blocks * page_size, D, num_splits, q.device)
         code = L.b200k_fmha_decode_paged(
             q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), B, Hq, Hkv, Sq, D, num_pages,
             page_size, _lib.strides3(q), _lib.strides3(k_pages), _lib.strides3(v_pages), _lib.strides3(out),
             float(scale), block_table.data_ptr(), max_blocks, kv_lens.data_ptr(), int(num_splits), _DTYPES[q.dtype],
-            ws.data_ptr(), ws.numel(), torch.cuda.current_stream(q.device).cuda_stream)
+            ws.data_ptr(), ws.numel(), _lib.raw_stream(q.device))
     _lib.check(code, "b200k_fmha_decode_paged")
     return out

@@ -45,12 +45,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, vari
     L = _lib.lib()
     dev_index = a.device.index
     if dev_index is not None and dev_index != torch.cuda.current_device():
-        with torch.cuda.device(a.device):
+        with _lib.on_device(a.device):
             return gemm(a, b, out=out, variant=variant)
     # no variant needs a workspace (split-K partials stay in shared memory), so none is allocated
     code = L.b200k_gemm(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K,
                         a.stride(0), b.stride(0), out.stride(0), _DTYPES[a.dtype], variant,
-                        None, 0, torch.cuda.current_stream().cuda_stream)
+                        None, 0, _lib.raw_stream(a.device))
     if code:
         _lib.check(code, "b200k_gemm")
     return out
@@ -86,11 +86,11 @@ def _fused(a, b, residual, epilogue, out):
             residual = residual.contiguous()
     if M == 0 or N == 0:
         return out
-    with torch.cuda.device(a.device):
+    with _lib.on_device(a.device):
         code = _lib.lib().b200k_gemm_fused(
             a.data_ptr(), b.data_ptr(), out.data_ptr(), residual.data_ptr() if residual is not None else None,
             M, N, K, a.stride(0), b.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
-            _DTYPES[a.dtype], epilogue, torch.cuda.current_stream(a.device).cuda_stream)
+            _DTYPES[a.dtype], epilogue, _lib.raw_stream(a.device))
     _lib.check(code, "b200k_gemm_fused")
     return out
 

@@ -162,7 +162,7 @@ class FusedAllGatherGemm:
             code = _lib.lib().b200k_gemm_scatter(
                 a.data_ptr(), b_slab.data_ptr(), dsts, self.world, self.M, e - s, a.size(1),
                 a.stride(0), b_slab.stride(0), self.N, _DTYPES[a.dtype],
-                torch.cuda.current_stream(a.device).cuda_stream)
+                _lib.raw_stream(a.device))
             _lib.check(code, "b200k_gemm_scatter")
         self.handle.barrier()
         return self.c_full
