@@ -237,15 +237,16 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       if (ok) umma_commit<1>(tmem_full);
     }
   } else if (warp < 2 + 4 * kSkDrainGroups) {
-    // drain TMEM (lane = weight column, TMEM column = activation row) into this CTA's fp32
-    // tile [row][kSkBN]: consecutive lanes write consecutive words.  Two groups of four warps (a warp
-    // reaches the TMEM lanes of quarter warp % 4) take alternate (128-column, row-chunk) pieces.
+    // drain TMEM (lane = weight column, TMEM column = activation row): to C directly, to the owners'
+    // receive buffers, or to this CTA's fp32 tile [row][kSkBN] (consecutive lanes, consecutive words).
+    // Two groups of four warps (a warp reaches the TMEM lanes of quarter warp % 4) take alternate
+    // (128-column, row-chunk) pieces.
     const int ew = warp & 3;
     const int grp = (warp - 2) >> 2;
     const bool have = kb_end > kb_begin;
     // Only one lane polls the accumulator barrier during the main loop; the other 255 draining threads
-    // park on a hardware named barrier (polling from eight warps cost the loader and the MMA thread
-    // about 10 % of the streaming rate).  The verdict travels through shared memory.
+    // park on a hardware named barrier and issue nothing until it opens.  The verdict travels through
+    // shared memory.
     volatile uint32_t* verdict = tmem_holder + 1;
     if (warp == 2 && lane == 0) {
       uint32_t good = 1;
@@ -283,7 +284,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         if (L::kPush && S > 1) {
           // Push this CTA's partial of column n into slot `rank` of the receive buffer of the CTA that
           // owns the column's 16-byte chunk: consecutive lanes, consecutive words (plain remote stores).
-          const int c = n >> 2;                                          // chunk of 4 columns, 0..31
+          const int c = n >> 2;                                          // chunk of 4 columns of the slab
           const int owner = ((c + 1) * (int)S - 1) / (kSkBN / 4);        // r with c_begin(r) <= c < c_end(r)
           const int c_first = owner * (kSkBN / 4) / (int)S;              // first chunk of the owner's slice
           const int wmax = 4 * ((kSkBN / 4 + (int)S - 1) / (int)S);      // floats per row of a slot
