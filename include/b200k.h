@@ -118,6 +118,10 @@ size_t b200k_gemm_workspace_bytes(int M, int N, int K, int variant);
  * causal != 0 masks key j for query i when j > i + (Skv - Sq) (identical to the
  * reference's top-left rule `q_idx < k_idx` when Sq == Skv).
  * kv_len (0 < kv_len <= Skv) masks keys j >= kv_len.
+ * variant: 0 = the library's choice (persistent kernel up to kv_len 4096, one work
+ * item per CTA beyond).  For ablation: 1..5 = one item per CTA with 0, 2, 4, 1, 3 of
+ * every 8 exponentials computed by a polynomial on the FMA pipe instead of the
+ * MUFU; 11..15 = the same five on the persistent kernel.  Other values: B200K_EARG.
  * Replaces `torch::Tensor finefmha_N(Q, K, V, causal, is_decode,
  * decode_length)` of the reference
  * (kernels/fmha/pkg/fmha_unified/csrc/semi/fmha_4_nv.cu:395-443,
