@@ -151,6 +151,27 @@ def test_skinny_cluster_sizes_and_epilogues(cuda_device, monkeypatch, shape, spl
         assert got.shape == (M, N // 2) and oracle.rel_frobenius(got, want) <= TOL
 
 
+@pytest.mark.parametrize("splits", [0, 1, 3])
+@pytest.mark.parametrize("M", [5, 64, 128])
+def test_skinny_strided_operands(cuda_device, monkeypatch, M, splits):
+    """Row-strided A, B and C (views into wider tensors, as the column-slab sharding produces them): the
+    weight-streaming kernel honours all three leading dimensions on its direct-store, push and pull
+    paths, and leaves the columns outside the output view untouched."""
+    from b200k import gemm
+    if splits:
+        monkeypatch.setenv("B200K_SKINNY_S", str(splits))
+    K, N = 520, 392
+    g = torch.Generator().manual_seed(M + splits)
+    a_big = torch.randn(M, K + 24, generator=g).to(torch.bfloat16).to(cuda_device)
+    b_big = (torch.randn(K, N + 40, generator=g) * 0.1).to(torch.bfloat16).to(cuda_device)
+    c_big = torch.full((M, N + 64), 7.0, dtype=torch.bfloat16, device=cuda_device)
+    a, b, c = a_big[:, 8:8 + K], b_big[:, 16:16 + N], c_big[:, 32:32 + N]
+    gemm.gemm(a, b, out=c, variant=3)
+    ref = oracle.gemm_ref(a.cpu(), b.cpu())
+    assert oracle.rel_frobenius(c, ref) <= TOL
+    assert bool((c_big[:, :32] == 7.0).all()) and bool((c_big[:, 32 + N:] == 7.0).all())
+
+
 def test_skinny_rejects_large_m(cuda_device):
     from b200k import _lib, gemm
     a = torch.zeros(256, 64, dtype=torch.float16, device=cuda_device)
