@@ -396,15 +396,20 @@ decode_reduce_kernel(const DecParams p, void* __restrict__ out, int64_t os0, int
     reinterpret_cast<__half*>(out)[off] = __float2half_rn(v);
 }
 
+// Splits per (batch, KV head).  Measured on B200 (graph-replayed, uniform and ragged lengths): every CTA
+// pays about 2-3 us of set-up and pipeline fill, so chunks should be long - about 4096 keys where the
+// (batch, head) pairs alone fill the GPU (the 64-sequence ragged batch: 7.0 TB/s with 4-8 splits, 6.7
+// with 32) - and where they do not, just enough splits for ONE wave of CTAs (8 sequences x 8 KV heads x
+// 8000 keys: 44 us with 2 splits = 128 CTAs, 52-55 us with 3 or 8; one sequence of 32768 keys: 28 us with
+// 12-16 splits, 34 us with 37).
 int choose_splits(int B, int Hkv, int Skv) {
   const int sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
-  const int by_size = (Skv + 1023) / 1024;
   const long pairs = (long)B * Hkv;
-  const int fill = (int)((2L * sms + pairs - 1) / pairs);
+  const int by_size = (Skv + 4095) / 4096;
+  const int fill = pairs < sms ? (int)(sms / pairs) : 1;
   const int max_by_tile = (Skv + 127) / 128;
-  int s = by_size;
-  const int f = fill < max_by_tile ? fill : max_by_tile;
-  if (f > s) s = f;
+  int s = by_size > fill ? by_size : fill;
+  if (s > max_by_tile) s = max_by_tile;
   if (s < 1) s = 1;
   if (s > 64) s = 64;
   return s;
