@@ -146,3 +146,54 @@ def test_paged_cache_matches_dense(cuda_device, page_size):
     paged = fmha.fmha_decode_paged(q, k_pages, v_pages, poisoned, lens, num_splits=4)
     assert torch.equal(paged, dense)
     assert oracle.max_abs(paged, oracle.fmha_ref(q, k, v, kv_lens=lens)) <= TOL
+
+
+@pytest.mark.parametrize("D,dtype", [(128, torch.float16), (64, torch.bfloat16)])
+@pytest.mark.parametrize("Hq,Hkv,splits", [(24, 6, 1), (8, 8, 1), (32, 8, 3)])
+def test_heads_grouped_per_cta_bit_identical(cuda_device, monkeypatch, Hq, Hkv, splits, D, dtype):
+    """A CTA may walk several KV heads of its sequence (the library groups heads by itself for
+    large batches of short sequences; B200K_DECODE_HEADS_PER_CTA forces a group size).  Every
+    grouping - including one that does not divide the head count and one larger than it - gives
+    the bits of one head per CTA, with ragged lengths, an empty sequence and NaN padding."""
+    from b200k import inputs
+    B, Skv = 5, 640
+    q, k, v = inputs.fmha_inputs(B, Hq, Hkv, 1, Skv, D, dtype, seed=Hq + splits)
+    lens = torch.tensor([640, 0, 1, 333, 64], dtype=torch.int32)
+    for b in range(B):
+        k[b, :, int(lens[b]):] = float("nan")
+        v[b, :, int(lens[b]):] = float("nan")
+    monkeypatch.setenv("B200K_DECODE_HEADS_PER_CTA", "1")
+    base = _decode(q, k, v, lens, cuda_device, num_splits=splits)
+    ref = oracle.fmha_ref(q, k, v, kv_lens=lens)
+    tol = TOL if dtype == torch.float16 else TOL + float(ref.abs().max()) * 2.0 ** -8
+    assert oracle.max_abs(base, ref) <= tol
+    assert torch.equal(base[1], torch.zeros_like(base[1]))
+    for h in (2, 4, 16):
+        monkeypatch.setenv("B200K_DECODE_HEADS_PER_CTA", str(h))
+        o = _decode(q, k, v, lens, cuda_device, num_splits=splits)
+        assert torch.equal(o.view(torch.int16), base.view(torch.int16)), h
+
+
+def test_single_split_writes_output_directly(cuda_device):
+    """With one split per sequence the split kernel normalises and writes O itself (one launch,
+    no partials); the result has the bits of the two-kernel path taken through a strided,
+    2-byte-aligned output view (scalar stores) as well as the contiguous one."""
+    from b200k import fmha, _lib, inputs
+    dev = cuda_device
+    B, Hq, Hkv, Skv, D = 37, 32, 8, 300, 128  # 37 x 8 = 296 CTAs: the library pairs heads by itself
+    q, k, v = inputs.fmha_inputs(B, Hq, Hkv, 1, Skv, D, torch.float16, seed=11)
+    lens = torch.randint(0, Skv + 1, (B,), generator=torch.Generator().manual_seed(5), dtype=torch.int32)
+    qd, kd, vd, ld = q.to(dev), k.to(dev), v.to(dev), lens.to(dev)
+    n0 = _lib.launch_count()
+    o1 = fmha.fmha_decode(qd, kd, vd, kv_lens=ld, num_splits=1)
+    assert _lib.launch_count() - n0 == 1
+    o2 = fmha.fmha_decode(qd, kd, vd, kv_lens=ld, num_splits=2)
+    assert _lib.launch_count() - n0 == 3
+    big = torch.full((B, Hq, 1, D + 2), 7.0, dtype=torch.float16, device=dev)
+    o3 = fmha.fmha_decode(qd, kd, vd, kv_lens=ld, num_splits=1, out=big[..., 1:D + 1])
+    torch.cuda.synchronize()
+    ref = oracle.fmha_ref(q, k, v, kv_lens=lens)
+    assert oracle.max_abs(o1.cpu(), ref) <= TOL
+    assert oracle.max_abs(o2.cpu(), ref) <= TOL
+    assert torch.equal(o3, o1)
+    assert torch.all(big[..., 0] == 7.0) and torch.all(big[..., D + 1] == 7.0)

@@ -12,8 +12,13 @@
 //     row statistics reduced across the 4 lanes of a quad with shuffles.
 //   * the 4 warps' states are merged through shared memory in a fixed order and written
 //     as one (max, sum, partial O) triple per (row, split) to the fp32 workspace;
-//   * a second kernel merges the splits of each row in a fixed order and writes 16-bit O.
-// Results are therefore bit-identical from run to run.
+//   * a second kernel merges the splits of each row in a fixed order and writes 16-bit O;
+//     with one split per sequence the first kernel normalises and writes O itself (same
+//     arithmetic, same bits; no partials, no second launch);
+//   * unsplit sequences in large batches: a CTA walks several KV heads of its sequence
+//     (grid.y = groups of heads), the ring never drains between them and the next head's Q
+//     is fetched under the current head's tiles.
+// Results are therefore bit-identical from run to run and across groupings.
 //
 // Reference semantics: is_decode = true of
 // kernels/fmha/pkg/fmha_unified/csrc/semi/fmha_4_nv.cu:240-243,415-417 (non-causal, keys
@@ -51,6 +56,11 @@ struct DecParams {
   const void* q;
   int64_t q_strides[3];
   const int32_t* kv_lens;
+  int heads_per_cta;  // consecutive KV heads one CTA walks (set-up once, the TMA ring never drains)
+  // num_splits == 1: the split kernel normalises and writes O itself (no partials, no second kernel)
+  void* out;
+  int64_t o_strides[3];
+  int out_vec;  // O base 8-byte aligned and strides multiples of 4 elements: 4 columns per store
   float* part_o;   // [B][Hkv][R][num_splits][D]
   float* part_ml;  // [B][Hkv][R][num_splits][2]
   int B, Hq, Hkv, Sq, Skv;
@@ -128,15 +138,33 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* empty_bar = full_bar + kDecStages;
+  // set by a consumer warp whose wait ran out; read by all four after a barrier so that they leave together
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + kDecStages);
   float* merge_o = reinterpret_cast<float*>(smem + L::kMergeOff);
   float* merge_ml = reinterpret_cast<float*>(smem + L::kMlOff);
 
-  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int split = blockIdx.x, b = blockIdx.z;
+  const int hk_first = blockIdx.y * p.heads_per_cta;
+  const int hk_last = min(p.Hkv, hk_first + p.heads_per_cta);  // exclusive
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int len = p.kv_lens ? p.kv_lens[b] : p.Skv;
   len = max(0, min(len, p.Skv));
   const int k_begin = split * p.chunk;
-  if (k_begin >= len) return;  // nothing for this split (uniform for the CTA)
+  if (k_begin >= len) {  // nothing for this split (uniform for the CTA)
+    if (p.out && split == 0) {
+      // an empty sequence still owns its rows of O: zeros, as the reduction kernel writes them
+      const int G0 = p.Hq / p.Hkv;
+      for (int i = threadIdx.x; i < (hk_last - hk_first) * p.rows * D; i += kDecThreads) {
+        const int hk = hk_first + i / (p.rows * D), j = i % (p.rows * D);
+        const int64_t off = row_offset(j / D, hk, b, G0, p.Sq, p.o_strides) + j % D;
+        if constexpr (BF16)
+          reinterpret_cast<__nv_bfloat16*>(p.out)[off] = __float2bfloat16_rn(0.f);
+        else
+          reinterpret_cast<__half*>(p.out)[off] = __float2half_rn(0.f);
+      }
+    }
+    return;
+  }
   const int k_end = min(len, k_begin + p.chunk);
   const int n_tiles = (k_end - k_begin + kDecTile - 1) / kDecTile;
 
@@ -145,6 +173,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 4);
     }
+    *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmK);
     prefetch_tmap(&tmV);
@@ -156,9 +185,12 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     // ------------------------------- TMA producer -------------------------------
     if (elect_one()) {
       uint32_t stage = 0, phase = 0;
+      bool alive = true;
+      for (int hk = hk_first; hk < hk_last && alive; ++hk)
       for (int t = 0; t < n_tiles; ++t) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
           report_timeout(p.status, KID_DECODE, ROLE_PRODUCER);
+          alive = false;
           break;
         }
         uint8_t* sk = smem + stage * L::kStageBytes;
@@ -187,9 +219,14 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     // -------------------------------- consumers ---------------------------------
     const int qrow = lane >> 2;  // MMA row of c[0], c[1]; c[2], c[3] are row qrow + 8
     const int qcol = (lane & 3) * 2;
+    const float sc = p.scale_log2;
+    // ldmatrix lane roles
+    const int mi = lane >> 3, mr = lane & 7;
+    // the ring's stage and phase run on across the heads this CTA walks
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
     // Q as the A operand: 8 k-steps of 16 d; rows >= R are zero.
-    uint32_t qa[D / 16][4];
-    {
+    auto load_q = [&](int hk, uint32_t (&dst)[D / 16][4]) {
       const uint16_t* qbase = reinterpret_cast<const uint16_t*>(p.q);
       const bool lo_ok = qrow < p.rows, hi_ok = qrow + 8 < p.rows;
       const int64_t off_lo = lo_ok ? row_offset(qrow, hk, b, G, p.Sq, p.q_strides) : 0;
@@ -197,25 +234,28 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
         const int d0 = ks * 16 + qcol;
-        qa[ks][0] = lo_ok ? *reinterpret_cast<const uint32_t*>(qbase + off_lo + d0) : 0u;
-        qa[ks][1] = hi_ok ? *reinterpret_cast<const uint32_t*>(qbase + off_hi + d0) : 0u;
-        qa[ks][2] = lo_ok ? *reinterpret_cast<const uint32_t*>(qbase + off_lo + d0 + 8) : 0u;
-        qa[ks][3] = hi_ok ? *reinterpret_cast<const uint32_t*>(qbase + off_hi + d0 + 8) : 0u;
+        dst[ks][0] = lo_ok ? *reinterpret_cast<const uint32_t*>(qbase + off_lo + d0) : 0u;
+        dst[ks][1] = hi_ok ? *reinterpret_cast<const uint32_t*>(qbase + off_hi + d0) : 0u;
+        dst[ks][2] = lo_ok ? *reinterpret_cast<const uint32_t*>(qbase + off_lo + d0 + 8) : 0u;
+        dst[ks][3] = hi_ok ? *reinterpret_cast<const uint32_t*>(qbase + off_hi + d0 + 8) : 0u;
       }
-    }
+    };
+    uint32_t qa[D / 16][4];
+    load_q(hk_first, qa);
+    for (int hk = hk_first; hk < hk_last; ++hk) {
+    // the next head's Q is fetched now, under this head's tiles
+    uint32_t qn[D / 16][4];
+    if (hk + 1 < hk_last) load_q(hk + 1, qn);
     float o[kDTiles][4];
 #pragma unroll
     for (int dt = 0; dt < kDTiles; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
-    const float sc = p.scale_log2;
-
-    uint32_t stage = 0, phase = 0;
-    bool ok = true;
-    // ldmatrix lane roles
-    const int mi = lane >> 3, mr = lane & 7;
     for (int t = 0; t < n_tiles; ++t) {
       if (!mbar_wait(&full_bar[stage], phase)) {
-        if (lane == 0) report_timeout(p.status, KID_DECODE, ROLE_MMA);
+        if (lane == 0) {
+          report_timeout(p.status, KID_DECODE, ROLE_MMA);
+          *abort_flag = 1;
+        }
         ok = false;
         break;
       }
@@ -316,7 +356,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         phase ^= 1;
       }
     }
-    (void)ok;
+    // a warp whose wait ran out still walks through the barriers below (its partials are garbage and the
+    // status word says so); the four warps then stop together
     // ---- quad-reduce the row sums, publish this warp's state ----
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
@@ -325,8 +366,10 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     float* mo = merge_o + warp * kMaxRows * D;
 #pragma unroll
     for (int dt = 0; dt < kDTiles; ++dt) {
-      *reinterpret_cast<float2*>(mo + qrow * D + dt * 8 + qcol) = make_float2(o[dt][0], o[dt][1]);
-      *reinterpret_cast<float2*>(mo + (qrow + 8) * D + dt * 8 + qcol) = make_float2(o[dt][2], o[dt][3]);
+      // column c of row r sits at c ^ ((r & 3) << 3): the 8 rows of a store spread over the banks
+      const int pc = (dt * 8 + qcol) ^ ((qrow & 3) << 3);
+      *reinterpret_cast<float2*>(mo + qrow * D + pc) = make_float2(o[dt][0], o[dt][1]);
+      *reinterpret_cast<float2*>(mo + (qrow + 8) * D + pc) = make_float2(o[dt][2], o[dt][3]);
     }
     if ((lane & 3) == 0) {
       float* ml = merge_ml + warp * kMaxRows * 2;
@@ -338,30 +381,63 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     named_barrier_sync(1, 128);
     // ---- merge the 4 warps in order 0..3 and write the partial triple ----
     const int tid = threadIdx.x;  // 0..127
-    for (int r = 0; r < p.rows; ++r) {
+    // one item = 4 consecutive columns of one row; GQA groups of up to 4 rows take one pass
+    for (int it = tid; it < p.rows * (D / 4); it += 128) {
+      const int r = it / (D / 4), c = (it % (D / 4)) * 4;
       float mstar = -INFINITY;
 #pragma unroll
       for (int w = 0; w < 4; ++w) mstar = fmaxf(mstar, merge_ml[(w * kMaxRows + r) * 2]);
       float lsum = 0.f;
-      float wgt[4];
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      const int pc = c ^ ((r & 3) << 3);
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
         const float mw = merge_ml[(w * kMaxRows + r) * 2];
-        wgt[w] = (mw == -INFINITY) ? 0.f : ex2f(mw - mstar);
-        lsum += merge_ml[(w * kMaxRows + r) * 2 + 1] * wgt[w];
+        const float wgt = (mw == -INFINITY) ? 0.f : ex2f(mw - mstar);
+        lsum += merge_ml[(w * kMaxRows + r) * 2 + 1] * wgt;
+        const float4 x = *reinterpret_cast<const float4*>(merge_o + (w * kMaxRows + r) * D + pc);
+        acc.x += x.x * wgt;
+        acc.y += x.y * wgt;
+        acc.z += x.z * wgt;
+        acc.w += x.w * wgt;
+      }
+      if (p.out) {
+        // single split: the same arithmetic the reduction kernel does on one partial (weight 2^0 = 1)
+        const int64_t off = row_offset(r, hk, b, G, p.Sq, p.o_strides) + c;
+        const float v0 = lsum > 0.f ? acc.x / lsum : 0.f, v1 = lsum > 0.f ? acc.y / lsum : 0.f;
+        const float v2 = lsum > 0.f ? acc.z / lsum : 0.f, v3 = lsum > 0.f ? acc.w / lsum : 0.f;
+        uint16_t* o16 = reinterpret_cast<uint16_t*>(p.out) + off;
+        const uint32_t lo = pack_p<BF16>(v0, v1), hi = pack_p<BF16>(v2, v3);
+        if (p.out_vec) {
+          *reinterpret_cast<uint2*>(o16) = make_uint2(lo, hi);
+        } else {
+          o16[0] = (uint16_t)lo;
+          o16[1] = (uint16_t)(lo >> 16);
+          o16[2] = (uint16_t)hi;
+          o16[3] = (uint16_t)(hi >> 16);
+        }
+        continue;
       }
       const int64_t prow = (((int64_t)b * p.Hkv + hk) * p.rows + r) * p.num_splits + split;
-      for (int d = tid; d < D; d += 128) {
-        float acc = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) acc += merge_o[(w * kMaxRows + r) * D + d] * wgt[w];
-        p.part_o[prow * D + d] = acc;
-      }
-      if (tid == 0) {
+      *reinterpret_cast<float4*>(p.part_o + prow * D + c) = acc;
+      if (c == 0) {
         p.part_ml[prow * 2 + 0] = mstar;
         p.part_ml[prow * 2 + 1] = lsum;
       }
     }
+    // the next head's warps rewrite the merge buffers: everybody must have read them
+    if (hk + 1 < hk_last) {
+      named_barrier_sync(1, 128);
+      if (*abort_flag) break;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        qa[ks][0] = qn[ks][0];
+        qa[ks][1] = qn[ks][1];
+        qa[ks][2] = qn[ks][2];
+        qa[ks][3] = qn[ks][3];
+      }
+    }
+    }  // heads
   }
 }
 
@@ -415,6 +491,34 @@ int choose_splits(int B, int Hkv, int Skv) {
   return s;
 }
 
+// KV heads one CTA walks (unsplit sequences only).  A CTA that takes several heads of its sequence sets up
+// once, keeps the TMA ring full across the heads and fetches the next head's Q under the current tiles.
+// Measured on B200 (bf16, d = 128, graph-replayed): what decides is how evenly the CTAs fill waves of one
+// per SM - 16 sequences x 32 heads x 4096 keys: 159 us with 512 CTAs, 152 us with 128 (4 heads each);
+// 512 x 8 x 256: 115 us with 4096 or 512 CTAs, 107 us with 1024; fewer CTAs than about 0.85 of the SMs
+// loses outright (8 x 32 x 2080 with 64 CTAs: 63 us against 44).  So: the largest power of two (at most 8,
+// dividing Hkv) among the groupings with the best wave efficiency n / (ceil(n / SMs) * SMs).
+int heads_per_cta(int B, int Hkv, int splits) {
+  // override for experiments and tests, read at every call (any value >= 1, also with split sequences)
+  const char* e = getenv("B200K_DECODE_HEADS_PER_CTA");
+  const int env = e ? atoi(e) : 0;
+  if (env >= 1) return env < Hkv ? env : Hkv;
+  if (splits != 1) return 1;
+  const long sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int h = 1; h <= 8 && h <= Hkv; h *= 2) {
+    if (Hkv % h) break;
+    const long n = (long)(Hkv / h) * B;
+    const double eff = (double)n / (double)((n + sms - 1) / sms * sms);
+    if (eff >= best_eff - 1e-9) {
+      best = h;
+      if (eff > best_eff) best_eff = eff;
+    }
+  }
+  return best;
+}
+
 int chunk_of(int Skv, int splits) {
   const int c = (Skv + splits - 1) / splits;
   return (c + kDecTile - 1) / kDecTile * kDecTile;
@@ -457,6 +561,11 @@ int launch_decode(const void* Q, const void* K, const void* V, void* O, int B, i
   p.kv_lens = kv_lens;
   p.part_o = part_o;
   p.part_ml = part_ml;
+  p.out = splits == 1 ? O : nullptr;
+  p.out_vec = (reinterpret_cast<uintptr_t>(O) & 7) == 0 && os[0] % 4 == 0 && os[1] % 4 == 0 && os[2] % 4 == 0;
+  p.o_strides[0] = os[0];
+  p.o_strides[1] = os[1];
+  p.o_strides[2] = os[2];
   p.B = B;
   p.Hq = Hq;
   p.Hkv = Hkv;
@@ -465,17 +574,18 @@ int launch_decode(const void* Q, const void* K, const void* V, void* O, int B, i
   p.rows = Hq / Hkv * Sq;
   p.num_splits = splits;
   p.chunk = chunk_of(Skv, splits);
+  p.heads_per_cta = heads_per_cta(B, Hkv, splits);
   p.scale_log2 = scale * 1.4426950408889634f;
   p.block_table = block_table;
   p.max_blocks = max_blocks;
   p.page_size = page_size;
   p.status = status_ptr();
   if (!p.status) return B200K_ECUDA;
-  dim3 grid(splits, Hkv, B);
+  dim3 grid(splits, (Hkv + p.heads_per_cta - 1) / p.heads_per_cta, B);
   kfn<<<grid, kDecThreads, L::kTotal, stream>>>(tmK, tmV, p);
   count_launch();
   int r = check_launch();
-  if (r) return r;
+  if (r || splits == 1) return r;
   decode_reduce_kernel<D, BF16><<<B * Hkv * p.rows, D, 0, stream>>>(p, O, os[0], os[1], os[2]);
   count_launch();
   return check_launch();
