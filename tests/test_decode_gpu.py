@@ -151,8 +151,8 @@ def test_paged_cache_matches_dense(cuda_device, page_size):
 @pytest.mark.parametrize("D,dtype", [(128, torch.float16), (64, torch.bfloat16)])
 @pytest.mark.parametrize("Hq,Hkv,splits", [(24, 6, 1), (8, 8, 1), (32, 8, 3)])
 def test_heads_grouped_per_cta_bit_identical(cuda_device, monkeypatch, Hq, Hkv, splits, D, dtype):
-    """A CTA may walk several KV heads of its sequence (the library groups heads by itself for
-    large batches of short sequences; B200K_DECODE_HEADS_PER_CTA forces a group size).  Every
+    """A CTA may walk several KV heads of its sequence (B200K_DECODE_HEADS_PER_CTA forces the
+    group size; the library's own work lists are covered by the single-split test below).  Every
     grouping - including one that does not divide the head count and one larger than it - gives
     the bits of one head per CTA, with ragged lengths, an empty sequence and NaN padding."""
     from b200k import inputs
@@ -174,15 +174,17 @@ def test_heads_grouped_per_cta_bit_identical(cuda_device, monkeypatch, Hq, Hkv, 
         assert torch.equal(o.view(torch.int16), base.view(torch.int16)), h
 
 
-def test_single_split_writes_output_directly(cuda_device):
+def test_single_split_writes_output_directly(cuda_device, monkeypatch):
     """With one split per sequence the split kernel normalises and writes O itself (one launch,
-    no partials); the result has the bits of the two-kernel path taken through a strided,
-    2-byte-aligned output view (scalar stores) as well as the contiguous one."""
+    no partials), and with more (sequence, head) pairs than SMs its CTAs walk strided lists of
+    pairs.  The result has the bits of one CTA per pair, also through a strided, 2-byte-aligned
+    output view (scalar stores), with ragged lengths and empty sequences in the lists."""
     from b200k import fmha, _lib, inputs
     dev = cuda_device
-    B, Hq, Hkv, Skv, D = 37, 32, 8, 300, 128  # 37 x 8 = 296 CTAs: the library pairs heads by itself
+    B, Hq, Hkv, Skv, D = 41, 32, 8, 300, 128  # 328 pairs on 148 SMs: lists of 2 or 3 pairs
     q, k, v = inputs.fmha_inputs(B, Hq, Hkv, 1, Skv, D, torch.float16, seed=11)
     lens = torch.randint(0, Skv + 1, (B,), generator=torch.Generator().manual_seed(5), dtype=torch.int32)
+    lens[0], lens[3], lens[B - 1], lens[7] = 0, 0, 0, Skv
     qd, kd, vd, ld = q.to(dev), k.to(dev), v.to(dev), lens.to(dev)
     n0 = _lib.launch_count()
     o1 = fmha.fmha_decode(qd, kd, vd, kv_lens=ld, num_splits=1)
@@ -197,3 +199,8 @@ def test_single_split_writes_output_directly(cuda_device):
     assert oracle.max_abs(o2.cpu(), ref) <= TOL
     assert torch.equal(o3, o1)
     assert torch.all(big[..., 0] == 7.0) and torch.all(big[..., D + 1] == 7.0)
+    monkeypatch.setenv("B200K_DECODE_HEADS_PER_CTA", "1")
+    o4 = fmha.fmha_decode(qd, kd, vd, kv_lens=ld, num_splits=1)
+    torch.cuda.synchronize()
+    assert torch.equal(o4, o1)
+    assert torch.equal(o1[0], torch.zeros_like(o1[0])) and torch.equal(o1[B - 1], torch.zeros_like(o1[0]))

@@ -15,10 +15,11 @@
 //   * a second kernel merges the splits of each row in a fixed order and writes 16-bit O;
 //     with one split per sequence the first kernel normalises and writes O itself (same
 //     arithmetic, same bits; no partials, no second launch);
-//   * unsplit sequences in large batches: a CTA walks several KV heads of its sequence
-//     (grid.y = groups of heads), the ring never drains between them and the next head's Q
-//     is fetched under the current head's tiles.
-// Results are therefore bit-identical from run to run and across groupings.
+//   * unsplit sequences, more (sequence, head) pairs than SMs: the grid is one wave of CTAs
+//     and each walks a strided list of pairs; the ring never drains between pairs and the
+//     next pair's Q and length are fetched under the current pair's tiles;
+//   * the last tile of a sequence is fetched in 16-key slices, only those that hold keys.
+// Results are therefore bit-identical from run to run and across work-list shapes.
 //
 // Reference semantics: is_decode = true of
 // kernels/fmha/pkg/fmha_unified/csrc/semi/fmha_4_nv.cu:240-243,415-417 (non-causal, keys
@@ -56,7 +57,8 @@ struct DecParams {
   const void* q;
   int64_t q_strides[3];
   const int32_t* kv_lens;
-  int heads_per_cta;  // consecutive KV heads one CTA walks (set-up once, the TMA ring never drains)
+  int heads_per_cta;  // consecutive KV heads of one sequence a CTA walks when item_stride == 0
+  int item_stride;    // > 0: CTA y walks items y, y + item_stride, ... of the B * Hkv (sequence, head) pairs
   // num_splits == 1: the split kernel normalises and writes O itself (no partials, no second kernel)
   void* out;
   int64_t o_strides[3];
@@ -130,6 +132,7 @@ __device__ __forceinline__ int64_t row_offset(int r, int hk, int b, int G, int S
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kDecThreads, 1)
 decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                      const __grid_constant__ CUtensorMap tmK16, const __grid_constant__ CUtensorMap tmV16,
                       const DecParams p) {
   using L = DecSmem<D>;
   constexpr int kDBoxes = D / 64;
@@ -143,30 +146,48 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   float* merge_o = reinterpret_cast<float*>(smem + L::kMergeOff);
   float* merge_ml = reinterpret_cast<float*>(smem + L::kMlOff);
 
-  const int split = blockIdx.x, b = blockIdx.z;
-  const int hk_first = blockIdx.y * p.heads_per_cta;
-  const int hk_last = min(p.Hkv, hk_first + p.heads_per_cta);  // exclusive
+  // The CTA's work list: items (sequence b, KV head hk) = b * Hkv + hk.
+  //   item_stride > 0 (unsplit sequences, one CTA per SM or fewer): items blockIdx.y, + stride, ...
+  //   item_stride = 0: heads_per_cta consecutive heads of sequence blockIdx.z
+  const int split = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int len = p.kv_lens ? p.kv_lens[b] : p.Skv;
-  len = max(0, min(len, p.Skv));
   const int k_begin = split * p.chunk;
-  if (k_begin >= len) {  // nothing for this split (uniform for the CTA)
-    if (p.out && split == 0) {
-      // an empty sequence still owns its rows of O: zeros, as the reduction kernel writes them
-      const int G0 = p.Hq / p.Hkv;
-      for (int i = threadIdx.x; i < (hk_last - hk_first) * p.rows * D; i += kDecThreads) {
-        const int hk = hk_first + i / (p.rows * D), j = i % (p.rows * D);
-        const int64_t off = row_offset(j / D, hk, b, G0, p.Sq, p.o_strides) + j % D;
-        if constexpr (BF16)
-          reinterpret_cast<__nv_bfloat16*>(p.out)[off] = __float2bfloat16_rn(0.f);
-        else
-          reinterpret_cast<__half*>(p.out)[off] = __float2half_rn(0.f);
-      }
-    }
-    return;
+  const int G = p.Hq / p.Hkv;
+  int item_first, item_end, item_stride;
+  if (p.item_stride > 0) {
+    item_first = blockIdx.y;
+    item_end = p.B * p.Hkv;
+    item_stride = p.item_stride;
+  } else {
+    const int hk_first = blockIdx.y * p.heads_per_cta;
+    item_first = blockIdx.z * p.Hkv + hk_first;
+    item_end = blockIdx.z * p.Hkv + min(p.Hkv, hk_first + p.heads_per_cta);
+    item_stride = 1;
   }
-  const int k_end = min(len, k_begin + p.chunk);
-  const int n_tiles = (k_end - k_begin + kDecTile - 1) / kDecTile;
+  auto raw_len = [&](int b) { return p.kv_lens ? p.kv_lens[b] : p.Skv; };
+  // tiles of this split in a sequence of (unclamped) length len; k_end = end of its keys
+  auto span = [&](int len, int& k_end) {
+    len = max(0, min(len, p.Skv));
+    k_end = min(len, k_begin + p.chunk);
+    return k_begin >= len ? 0 : (k_end - k_begin + kDecTile - 1) / kDecTile;
+  };
+  // an empty sequence still owns its rows of O in single-split mode: zeros, as the reduction kernel writes
+  auto zero_rows = [&](int b, int hk, int tid, int nthreads) {
+    for (int i = tid; i < p.rows * D; i += nthreads) {
+      const int64_t off = row_offset(i / D, hk, b, G, p.Sq, p.o_strides) + i % D;
+      reinterpret_cast<uint16_t*>(p.out)[off] = 0;  // +0 in fp16 and bf16
+    }
+  };
+  if (p.item_stride == 0) {
+    // all items share the sequence: a split beyond its length has nothing to do (uniform for the CTA)
+    int k_end_unused;
+    if (span(raw_len(blockIdx.z), k_end_unused) == 0) {
+      if (p.out && split == 0)
+        for (int item = item_first; item < item_end; ++item)
+          zero_rows(blockIdx.z, item % p.Hkv, threadIdx.x, kDecThreads);
+      return;
+    }
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kDecStages; ++s) {
@@ -177,16 +198,20 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     fence_mbar_init();
     prefetch_tmap(&tmK);
     prefetch_tmap(&tmV);
+    prefetch_tmap(&tmK16);
+    prefetch_tmap(&tmV16);
   }
   __syncthreads();
 
-  const int G = p.Hq / p.Hkv;
   if (warp == 4) {
     // ------------------------------- TMA producer -------------------------------
     if (elect_one()) {
       uint32_t stage = 0, phase = 0;
       bool alive = true;
-      for (int hk = hk_first; hk < hk_last && alive; ++hk)
+      for (int item = item_first; item < item_end && alive; item += item_stride) {
+      const int b = item / p.Hkv, hk = item % p.Hkv;
+      int k_end;
+      const int n_tiles = span(raw_len(b), k_end);
       for (int t = 0; t < n_tiles; ++t) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
           report_timeout(p.status, KID_DECODE, ROLE_PRODUCER);
@@ -195,25 +220,45 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         }
         uint8_t* sk = smem + stage * L::kStageBytes;
         uint8_t* sv = sk + L::kTileBytes;
-        mbar_expect_tx(&full_bar[stage], L::kStageBytes);
         int key0 = k_begin + t * kDecTile;
+        const int rows_left = k_end - key0;  // >= 1
         int outer = b;
         if (p.block_table) {
           // a 64-key tile never straddles pages; an out-of-range page index makes TMA read zeros
           outer = p.block_table[(int64_t)b * p.max_blocks + key0 / p.page_size];
           key0 %= p.page_size;
         }
+        if (rows_left > kDecTile - 16) {
+          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
 #pragma unroll
-        for (int d = 0; d < kDBoxes; ++d)
-          tma_load_4d(sk + d * L::kHalfBytes, &tmK, &full_bar[stage], d * 64, key0, hk, outer);
+          for (int d = 0; d < kDBoxes; ++d)
+            tma_load_4d(sk + d * L::kHalfBytes, &tmK, &full_bar[stage], d * 64, key0, hk, outer);
 #pragma unroll
-        for (int d = 0; d < kDBoxes; ++d)
-          tma_load_4d(sv + d * L::kHalfBytes, &tmV, &full_bar[stage], d * 64, key0, hk, outer);
+          for (int d = 0; d < kDBoxes; ++d)
+            tma_load_4d(sv + d * L::kHalfBytes, &tmV, &full_bar[stage], d * 64, key0, hk, outer);
+        } else {
+          // last tile of a sequence with at most 48 keys left: fetch only the 16-key slices that hold
+          // keys (same shared-memory image; the slices left alone keep stale data, which the consumers
+          // mask in S and zero in V like any key beyond the length)
+          const int n16 = (rows_left + 15) / 16;
+          mbar_expect_tx(&full_bar[stage], (uint32_t)n16 * 2u * 16u * D * 2u);
+          for (int j = 0; j < n16; ++j) {
+#pragma unroll
+            for (int d = 0; d < kDBoxes; ++d)
+              tma_load_4d(sk + d * L::kHalfBytes + j * 16 * 128, &tmK16, &full_bar[stage], d * 64, key0 + 16 * j,
+                          hk, outer);
+#pragma unroll
+            for (int d = 0; d < kDBoxes; ++d)
+              tma_load_4d(sv + d * L::kHalfBytes + j * 16 * 128, &tmV16, &full_bar[stage], d * 64, key0 + 16 * j,
+                          hk, outer);
+          }
+        }
         if (++stage == kDecStages) {
           stage = 0;
           phase ^= 1;
         }
       }
+      }  // items
     }
   } else {
     // -------------------------------- consumers ---------------------------------
@@ -226,7 +271,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     uint32_t stage = 0, phase = 0;
     bool ok = true;
     // Q as the A operand: 8 k-steps of 16 d; rows >= R are zero.
-    auto load_q = [&](int hk, uint32_t (&dst)[D / 16][4]) {
+    auto load_q = [&](int b, int hk, uint32_t (&dst)[D / 16][4]) {
       const uint16_t* qbase = reinterpret_cast<const uint16_t*>(p.q);
       const bool lo_ok = qrow < p.rows, hi_ok = qrow + 8 < p.rows;
       const int64_t off_lo = lo_ok ? row_offset(qrow, hk, b, G, p.Sq, p.q_strides) : 0;
@@ -241,11 +286,24 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       }
     };
     uint32_t qa[D / 16][4];
-    load_q(hk_first, qa);
-    for (int hk = hk_first; hk < hk_last; ++hk) {
-    // the next head's Q is fetched now, under this head's tiles
+    int b = item_first / p.Hkv, hk = item_first % p.Hkv;
+    load_q(b, hk, qa);
+    int k_end;
+    int n_tiles = span(raw_len(b), k_end);
+    for (int item = item_first; item < item_end; item += item_stride) {
+    // the next item's Q and length are fetched now, under this item's tiles
+    const bool has_next = item + item_stride < item_end;
+    const int nb = has_next ? (item + item_stride) / p.Hkv : b;
+    const int nhk = has_next ? (item + item_stride) % p.Hkv : hk;
     uint32_t qn[D / 16][4];
-    if (hk + 1 < hk_last) load_q(hk + 1, qn);
+    int next_len = 0;
+    if (has_next) {
+      load_q(nb, nhk, qn);
+      next_len = raw_len(nb);
+    }
+    if (n_tiles == 0) {
+      if (p.out && split == 0) zero_rows(b, hk, threadIdx.x, 128);
+    } else {
     float o[kDTiles][4];
 #pragma unroll
     for (int dt = 0; dt < kDTiles; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
@@ -367,9 +425,11 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
 #pragma unroll
     for (int dt = 0; dt < kDTiles; ++dt) {
       // column c of row r sits at c ^ ((r & 3) << 3): the 8 rows of a store spread over the banks
+      // (rows beyond the group's are MMA padding: nobody reads them)
       const int pc = (dt * 8 + qcol) ^ ((qrow & 3) << 3);
-      *reinterpret_cast<float2*>(mo + qrow * D + pc) = make_float2(o[dt][0], o[dt][1]);
-      *reinterpret_cast<float2*>(mo + (qrow + 8) * D + pc) = make_float2(o[dt][2], o[dt][3]);
+      if (qrow < p.rows) *reinterpret_cast<float2*>(mo + qrow * D + pc) = make_float2(o[dt][0], o[dt][1]);
+      if (qrow + 8 < p.rows)
+        *reinterpret_cast<float2*>(mo + (qrow + 8) * D + pc) = make_float2(o[dt][2], o[dt][3]);
     }
     if ((lane & 3) == 0) {
       float* ml = merge_ml + warp * kMaxRows * 2;
@@ -425,10 +485,13 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         p.part_ml[prow * 2 + 1] = lsum;
       }
     }
-    // the next head's warps rewrite the merge buffers: everybody must have read them
-    if (hk + 1 < hk_last) {
+    // the next item's warps rewrite the merge buffers: everybody must have read them
+    if (has_next) {
       named_barrier_sync(1, 128);
       if (*abort_flag) break;
+    }
+    }  // item with keys
+    if (has_next) {
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
         qa[ks][0] = qn[ks][0];
@@ -436,8 +499,11 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         qa[ks][2] = qn[ks][2];
         qa[ks][3] = qn[ks][3];
       }
+      b = nb;
+      hk = nhk;
+      n_tiles = span(next_len, k_end);
     }
-    }  // heads
+    }  // items
   }
 }
 
@@ -491,32 +557,31 @@ int choose_splits(int B, int Hkv, int Skv) {
   return s;
 }
 
-// KV heads one CTA walks (unsplit sequences only).  A CTA that takes several heads of its sequence sets up
-// once, keeps the TMA ring full across the heads and fetches the next head's Q under the current tiles.
-// Measured on B200 (bf16, d = 128, graph-replayed): what decides is how evenly the CTAs fill waves of one
-// per SM - 16 sequences x 32 heads x 4096 keys: 159 us with 512 CTAs, 152 us with 128 (4 heads each);
-// 512 x 8 x 256: 115 us with 4096 or 512 CTAs, 107 us with 1024; fewer CTAs than about 0.85 of the SMs
-// loses outright (8 x 32 x 2080 with 64 CTAs: 63 us against 44).  So: the largest power of two (at most 8,
-// dividing Hkv) among the groupings with the best wave efficiency n / (ceil(n / SMs) * SMs).
-int heads_per_cta(int B, int Hkv, int splits) {
-  // override for experiments and tests, read at every call (any value >= 1, also with split sequences)
+// Work lists of the split kernel's CTAs for unsplit sequences.  Measured on B200 (bf16, d = 128,
+// graph-replayed): what decides is how evenly the CTAs fill waves of one per SM and how often a CTA
+// pays its set-up (launch, barriers, first round trip to HBM: 2-3 us) - 16 sequences x 32 heads x 4096
+// keys: 159 us with 512 CTAs, 152 us with 128 CTAs of 4 heads each; 512 x 8 x 256: 115 us with 4096 or
+// 512 CTAs, 107 us with 1024; fewer CTAs than about 0.85 of the SMs loses outright (8 x 32 x 2080 with
+// 64 CTAs: 63 us against 44).  So with more (sequence, head) pairs than SMs the grid is one wave of
+// CTAs and CTA y walks pairs y, y + G, y + 2G, ... (neighbouring CTAs take the heads of one sequence, a
+// CTA's pairs come from sequences spread over the batch, which evens out ragged lengths), with
+// G = ceil(pairs / ceil(pairs / SMs)) so that every CTA gets the same count up to one.
+int item_stride_of(int B, int Hkv, int splits) {
+  if (splits != 1) return 0;
+  const long sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
+  const long pairs = (long)B * Hkv;
+  if (pairs <= sms) return 0;
+  const long per_cta = (pairs + sms - 1) / sms;
+  return (int)((pairs + per_cta - 1) / per_cta);
+}
+
+// Override for experiments and tests, read at every call: B200K_DECODE_HEADS_PER_CTA = h >= 1 gives the
+// grid (split, groups of h consecutive KV heads, sequence) instead, also with split sequences.
+int heads_per_cta_override(int Hkv) {
   const char* e = getenv("B200K_DECODE_HEADS_PER_CTA");
   const int env = e ? atoi(e) : 0;
-  if (env >= 1) return env < Hkv ? env : Hkv;
-  if (splits != 1) return 1;
-  const long sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
-  int best = 1;
-  double best_eff = 0.0;
-  for (int h = 1; h <= 8 && h <= Hkv; h *= 2) {
-    if (Hkv % h) break;
-    const long n = (long)(Hkv / h) * B;
-    const double eff = (double)n / (double)((n + sms - 1) / sms * sms);
-    if (eff >= best_eff - 1e-9) {
-      best = h;
-      if (eff > best_eff) best_eff = eff;
-    }
-  }
-  return best;
+  if (env < 1) return 0;
+  return env < Hkv ? env : Hkv;
 }
 
 int chunk_of(int Skv, int splits) {
@@ -541,7 +606,7 @@ int launch_decode(const void* Q, const void* K, const void* V, void* O, int B, i
     }
     configured[dev & 63] = true;
   }
-  CUtensorMap tmK, tmV;
+  CUtensorMap tmK, tmV, tmK16, tmV16;  // 64-key boxes; 16-key boxes for the tail of a sequence
   {
     // contiguous: (D, Skv, Hkv, B); paged: (D, page_size, Hkv, num_pages) with Skv = max_blocks * page_size
     uint64_t dims[4] = {(uint64_t)D, (uint64_t)(block_table ? page_size : Skv), (uint64_t)Hkv,
@@ -552,6 +617,9 @@ int launch_decode(const void* Q, const void* K, const void* V, void* O, int B, i
     int r;
     if ((r = encode_tmap_16bit(&tmK, K, 4, dims, kstr, box, 1))) return r;
     if ((r = encode_tmap_16bit(&tmV, V, 4, dims, vstr, box, 1))) return r;
+    uint32_t box16[4] = {64, 16, 1, 1};
+    if ((r = encode_tmap_16bit(&tmK16, K, 4, dims, kstr, box16, 1))) return r;
+    if ((r = encode_tmap_16bit(&tmV16, V, 4, dims, vstr, box16, 1))) return r;
   }
   DecParams p;
   p.q = Q;
@@ -574,15 +642,18 @@ int launch_decode(const void* Q, const void* K, const void* V, void* O, int B, i
   p.rows = Hq / Hkv * Sq;
   p.num_splits = splits;
   p.chunk = chunk_of(Skv, splits);
-  p.heads_per_cta = heads_per_cta(B, Hkv, splits);
+  const int forced = heads_per_cta_override(Hkv);
+  p.heads_per_cta = forced ? forced : 1;
+  p.item_stride = forced ? 0 : item_stride_of(B, Hkv, splits);
   p.scale_log2 = scale * 1.4426950408889634f;
   p.block_table = block_table;
   p.max_blocks = max_blocks;
   p.page_size = page_size;
   p.status = status_ptr();
   if (!p.status) return B200K_ECUDA;
-  dim3 grid(splits, (Hkv + p.heads_per_cta - 1) / p.heads_per_cta, B);
-  kfn<<<grid, kDecThreads, L::kTotal, stream>>>(tmK, tmV, p);
+  const dim3 grid = p.item_stride > 0 ? dim3(1, p.item_stride, 1)
+                                      : dim3(splits, (Hkv + p.heads_per_cta - 1) / p.heads_per_cta, B);
+  kfn<<<grid, kDecThreads, L::kTotal, stream>>>(tmK, tmV, tmK16, tmV16, p);
   count_launch();
   int r = check_launch();
   if (r || splits == 1) return r;
