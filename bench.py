@@ -260,6 +260,18 @@ def run_profile_case(args):
         ws = fmha.decode_workspace(B, Hq, Hkv, 1, Skv, D, 0, dev)
         fn = lambda: fmha.fmha_decode(q, k, v, kv_lens=lens, out=o, workspace=ws)
         work, unit = (float(lens.sum().item()) * Hkv * D * 4 + 2.0 * B * Hq * D * 2) / 1e9, "GB/s"
+    elif case == "decode_short":
+        # a large batch of short sequences: every sequence unsplit, the split kernel walks strided lists of
+        # (sequence, head) pairs and writes O itself; 0.5 GiB of K+V
+        B, Hq, Hkv, Skv, D = 512, 32, 8, 256, 128
+        lens = torch.full((B,), Skv, dtype=torch.int32, device=dev)
+        q = inputs.device_randn16((B, Hq, 1, D), 7, 1.0, torch.bfloat16, dev)
+        k = inputs.device_randn16((B, Hkv, Skv, D), 8, 1.0, torch.bfloat16, dev)
+        v = inputs.device_randn16((B, Hkv, Skv, D), 9, 1.0, torch.bfloat16, dev)
+        o = torch.empty_like(q)
+        ws = fmha.decode_workspace(B, Hq, Hkv, 1, Skv, D, 0, dev)
+        fn = lambda: fmha.fmha_decode(q, k, v, kv_lens=lens, out=o, workspace=ws)
+        work, unit = (float(B) * Skv * Hkv * D * 4 + 2.0 * B * Hq * D * 2) / 1e9, "GB/s"
     elif case == "skinny":
         # the decode pairing: 64 rows against the 4096 x 11008 weight, four copies in rotation so that
         # every launch streams its weight from HBM (one copy, 90 MB, would sit in the 126 MB L2)
@@ -589,7 +601,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "fmha", "decode", "skinny"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "fmha", "decode", "decode_short", "skinny"],
                     help="run only this path on a capture-sized case (for ncu); prints its own short line")
     ap.add_argument("--variant", type=int, default=0, help="GEMM kernel variant for --profile-case gemm")
     args = ap.parse_args()

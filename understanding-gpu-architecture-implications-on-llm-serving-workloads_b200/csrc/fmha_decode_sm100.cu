@@ -49,7 +49,11 @@ struct DecSmem {
   static constexpr uint32_t kMergeOff = kDecStages * kStageBytes;  // fp32 [4 warps][16 rows][D]
   static constexpr uint32_t kMergeBytes = 4 * kMaxRows * D * 4;
   static constexpr uint32_t kMlOff = kMergeOff + kMergeBytes;      // fp32 [4 warps][16 rows][2]
-  static constexpr uint32_t kBarOff = kMlOff + 4 * kMaxRows * 2 * 4;
+  // the next item's Q, copied asynchronously under the current item's tiles: 16-bit [2][16 rows][D + 8]
+  // (rows 16 bytes apart in the banks: the fragment loads of the 8 row groups do not collide)
+  static constexpr uint32_t kQOff = kMlOff + 4 * kMaxRows * 2 * 4;
+  static constexpr uint32_t kQRow = D + 8;
+  static constexpr uint32_t kBarOff = kQOff + 2 * kMaxRows * kQRow * 2;
   static constexpr uint32_t kTotal = kBarOff + 128 + 1024;
 };
 
@@ -85,6 +89,11 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
+__device__ __forceinline__ void cp_async_4(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
@@ -208,10 +217,15 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     if (elect_one()) {
       uint32_t stage = 0, phase = 0;
       bool alive = true;
+      // the length of the next item is asked for one item ahead: its latency must not sit between the
+      // last tile of one item and the first of the next
+      int cur_len = raw_len(item_first / p.Hkv);
       for (int item = item_first; item < item_end && alive; item += item_stride) {
       const int b = item / p.Hkv, hk = item % p.Hkv;
+      const int next_len = item + item_stride < item_end ? raw_len((item + item_stride) / p.Hkv) : 0;
       int k_end;
-      const int n_tiles = span(raw_len(b), k_end);
+      const int n_tiles = span(cur_len, k_end);
+      cur_len = next_len;
       for (int t = 0; t < n_tiles; ++t) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
           report_timeout(p.status, KID_DECODE, ROLE_PRODUCER);
@@ -285,6 +299,32 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         dst[ks][3] = hi_ok ? *reinterpret_cast<const uint32_t*>(qbase + off_hi + d0 + 8) : 0u;
       }
     };
+    // The following items' Q come through shared memory: a register prefetch is free to be scheduled at
+    // its use, and then every item starts with a round trip to HBM (measured: 0.6-0.9 us per item).
+    uint16_t* q_stage = reinterpret_cast<uint16_t*>(smem + L::kQOff);
+    auto q_copy_async = [&](int b, int hk, int buf) {
+      const uint16_t* qbase = reinterpret_cast<const uint16_t*>(p.q);
+      for (int i = threadIdx.x; i < p.rows * (D / 2); i += 128) {
+        const int r = i / (D / 2), w = i % (D / 2);
+        cp_async_4(smem_u32(q_stage + (buf * kMaxRows + r) * L::kQRow + 2 * w),
+                   qbase + row_offset(r, hk, b, G, p.Sq, p.q_strides) + 2 * w);
+      }
+      cp_async_commit();
+    };
+    auto q_from_stage = [&](int buf, uint32_t (&dst)[D / 16][4]) {
+      const bool lo_ok = qrow < p.rows, hi_ok = qrow + 8 < p.rows;
+      const uint16_t* lo = q_stage + (buf * kMaxRows + qrow) * L::kQRow;
+      const uint16_t* hi = lo + 8 * L::kQRow;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const int d0 = ks * 16 + qcol;
+        dst[ks][0] = lo_ok ? *reinterpret_cast<const uint32_t*>(lo + d0) : 0u;
+        dst[ks][1] = hi_ok ? *reinterpret_cast<const uint32_t*>(hi + d0) : 0u;
+        dst[ks][2] = lo_ok ? *reinterpret_cast<const uint32_t*>(lo + d0 + 8) : 0u;
+        dst[ks][3] = hi_ok ? *reinterpret_cast<const uint32_t*>(hi + d0 + 8) : 0u;
+      }
+    };
+    int q_buf = 0;
     uint32_t qa[D / 16][4];
     int b = item_first / p.Hkv, hk = item_first % p.Hkv;
     load_q(b, hk, qa);
@@ -295,10 +335,9 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     const bool has_next = item + item_stride < item_end;
     const int nb = has_next ? (item + item_stride) / p.Hkv : b;
     const int nhk = has_next ? (item + item_stride) % p.Hkv : hk;
-    uint32_t qn[D / 16][4];
     int next_len = 0;
     if (has_next) {
-      load_q(nb, nhk, qn);
+      q_copy_async(nb, nhk, q_buf);
       next_len = raw_len(nb);
     }
     if (n_tiles == 0) {
@@ -485,20 +524,15 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         p.part_ml[prow * 2 + 1] = lsum;
       }
     }
-    // the next item's warps rewrite the merge buffers: everybody must have read them
-    if (has_next) {
-      named_barrier_sync(1, 128);
-      if (*abort_flag) break;
-    }
     }  // item with keys
     if (has_next) {
-#pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
-        qa[ks][0] = qn[ks][0];
-        qa[ks][1] = qn[ks][1];
-        qa[ks][2] = qn[ks][2];
-        qa[ks][3] = qn[ks][3];
-      }
+      // the next item's warps rewrite the merge buffers: everybody must have read them; and everybody's
+      // part of the next Q must have landed
+      cp_async_wait_all();
+      named_barrier_sync(1, 128);
+      if (*abort_flag) break;
+      q_from_stage(q_buf, qa);
+      q_buf ^= 1;
       b = nb;
       hk = nhk;
       n_tiles = span(next_len, k_end);
