@@ -143,7 +143,9 @@ int b200k_fmha_fwd(const void* Q_device, const void* K_device, const void* V_dev
  * kv_lens_device: int32[B] on the device with the valid length of each
  * sequence, or NULL for Skv everywhere.  num_splits = 0 lets the library
  * choose.  The workspace holds the partial triples
- * (b200k_fmha_decode_workspace_bytes).
+ * (b200k_fmha_decode_workspace_bytes).  With one split per sequence (chosen
+ * when the (batch, kv-head) pairs alone fill the GPU, or asked for) the first
+ * kernel writes O itself and the workspace, still required, stays untouched.
  * Has the same reference counterpart as b200k_fmha_fwd with is_decode = true
  * (kernels/fmha/pkg/fmha_unified/csrc/semi/fmha_4_nv.cu:240-243,415-417); the
  * per-sequence length vector is an addition, the reference passes one scalar
