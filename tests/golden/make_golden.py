@@ -13,26 +13,42 @@ time, and these fixtures freeze what those calls return so the repo's oracle
         active line compares against raw QK^T instead, a debugging leftover at :52;
         the function it defines and names as the oracle is what is frozen here.)
 
-Run from the repo root:  python tests/golden/make_golden.py
+`torch_attn` is not restated here: it is IMPORTED from the reference checkout
+(kernels/fmha/test/perf.py:10-24, the same function as kernels/fmha/test/correct.py:10-24;
+perf.py keeps its sweep behind `if __name__ == "__main__"`, correct.py runs a GPU check
+at import, so perf.py is the importable one).  Its module-level `import fmha_unified`
+resolves to the drop-in package of this repo; nothing of that package is called.
+
+Run from the repo root:  python tests/golden/make_golden.py /path/to/reference
+(or with REFERENCE_ROOT set).  The fixtures travel with the repo; the reference
+checkout is only needed to regenerate them.
 """
+import importlib.util
 import os
+import sys
 
 import numpy as np
 import torch
-from torch.nn import functional as F
 
 OUT = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(OUT))
+PKG = os.path.join(ROOT, "understanding-gpu-architecture-implications-on-llm-serving-workloads_b200")
 
 
-def repeat_kv(x: torch.Tensor, n_rep: int) -> torch.Tensor:
-    # what kernels/fmha/test/correct.py:11-20 does: each KV head repeated n_rep times in place
-    return x if n_rep == 1 else torch.repeat_interleave(x, n_rep, dim=1)
+def load_reference_torch_attn(reference_root: str):
+    """The reference test scripts' oracle function, imported from the checkout."""
+    path = os.path.join(reference_root, "kernels", "fmha", "test", "perf.py")
+    if not os.path.exists(path):
+        sys.exit(f"{path} not found: pass the reference checkout as the first argument or set REFERENCE_ROOT")
+    if PKG not in sys.path:
+        sys.path.insert(0, PKG)  # perf.py imports fmha_unified at module level
+    spec = importlib.util.spec_from_file_location("reference_fmha_perf", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.torch_attn
 
 
-def torch_attn(q, k, v, is_causal):
-    if q.size(1) != k.size(1):
-        k, v = repeat_kv(k, 4), repeat_kv(v, 4)
-    return F.scaled_dot_product_attention(q, k, v, is_causal=is_causal)
+torch_attn = None  # bound in __main__
 
 
 def gemm_case():
@@ -60,6 +76,7 @@ def fmha_case(name, gqa, causal, decode, dtype):
 
 
 if __name__ == "__main__":
+    torch_attn = load_reference_torch_attn(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_ROOT", ""))
     gemm_case()
     fmha_case("fmha_seed42_mha_causal_f16", False, True, False, torch.half)
     fmha_case("fmha_seed42_gqa_causal_f16", True, True, False, torch.half)

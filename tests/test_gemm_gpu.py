@@ -113,6 +113,27 @@ def test_config2_llm_shapes_rows(cuda_device, M, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("KN", [(4096, 4096), (4096, 11008), (11008, 4096), (4096, 12288)])
+def test_config2_m8192_all_weights(cuda_device, KN, dtype):
+    """M = 8192 tokens against each of the four Llama-2-7B-shaped weights, both dtypes, at full size:
+    operands drawn on the device (activations N(0,1), weights N(0,0.02)), a sample of rows (tile edges,
+    first and last) copied back and checked on the CPU against the fp32 matmul over all N columns; the
+    reference-facing op gives the same bits as the C-ABI wrapper."""
+    from b200k import gemm, inputs
+    import gemm_unified
+    K, N = KN
+    M = 8192
+    a = inputs.device_randn16((M, K), 500 + K, 1.0, dtype, cuda_device)
+    w = inputs.device_randn16((K, N), 600 + N, 0.02, dtype, cuda_device)
+    c = gemm.gemm(a, w)
+    rows = torch.tensor([0, 127, 128, 255, 256, 4095, 4096, 8000, 8190, 8191])
+    ref = oracle.gemm_ref(a[rows].cpu(), w.cpu())
+    err = oracle.rel_frobenius(c[rows], ref)
+    assert err <= TOL, err
+    assert torch.equal(gemm_unified.ops.fine_gemm(a, w, 12), c)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(1, 128, 64), (16, 256, 4096), (64, 4096, 4096), (128, 1000, 2048), (7, 136, 200),
                                    (33, 11008, 4096), (100, 520, 11008)])
 def test_skinny_split_k_clusters(cuda_device, shape, dtype):
@@ -170,6 +191,36 @@ def test_skinny_strided_operands(cuda_device, monkeypatch, M, splits):
     ref = oracle.gemm_ref(a.cpu(), b.cpu())
     assert oracle.rel_frobenius(c, ref) <= TOL
     assert bool((c_big[:, :32] == 7.0).all()) and bool((c_big[:, 32 + N:] == 7.0).all())
+
+
+@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("N", [130, 134, 263, 517])
+@pytest.mark.parametrize("M", [3, 64, 128])
+def test_skinny_column_window_ragged_n(cuda_device, monkeypatch, M, N, splits):
+    """C (and the residual R) as the first N columns of a wider tensor with N not a multiple of 4 (nor
+    of 2): the weight-streaming kernel's 4-wide (split-K) and 2-wide (single CTA) stores must stop at
+    column N, and the fused add must not read R beyond it."""
+    from b200k import gemm
+    monkeypatch.setenv("B200K_SKINNY_S", str(splits))
+    K = 264
+    a, b = _inputs(M, N, K, torch.bfloat16, seed=M + N, std_b=0.1)
+    wide = (N + 15) // 8 * 8 + 8
+    bd = torch.zeros(K, wide, dtype=torch.bfloat16, device=cuda_device)
+    bd[:, :N] = b.to(cuda_device)
+    big = torch.full((M, wide), 7.0, dtype=torch.bfloat16, device=cuda_device)
+    gemm.gemm(a.to(cuda_device), bd[:, :N], out=big[:, :N], variant=3)
+    ref = oracle.gemm_ref(a, b)
+    assert oracle.rel_frobenius(big[:, :N], ref) <= TOL
+    assert bool((big[:, N:] == 7.0).all())
+    rbig = torch.full((M, wide), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    g = torch.Generator().manual_seed(N)
+    r = torch.randn(M, N, generator=g).to(torch.bfloat16)
+    rbig[:, :N] = r.to(cuda_device)
+    big.fill_(7.0)
+    gemm.gemm_add(a.to(cuda_device), bd[:, :N], rbig[:, :N], out=big[:, :N])
+    assert not torch.isnan(big).any()
+    assert oracle.rel_frobenius(big[:, :N], ref + r.float()) <= TOL
+    assert bool((big[:, N:] == 7.0).all())
 
 
 def test_skinny_rejects_large_m(cuda_device):

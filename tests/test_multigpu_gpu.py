@@ -29,10 +29,28 @@ def _worker(rank, world, port, results):
         ok &= torch.equal(gathered, full)
         fused = shard.FusedAllGatherGemm(M, N, torch.bfloat16, dev)
         s, e = slabs[rank]
-        for _ in range(2):  # twice: the symmetric buffer is reused
-            c = fused(a, w[:, s:e])
-            torch.cuda.synchronize()
-            ok &= torch.equal(c, full)
+        # Back-to-back calls with DIFFERENT activations and no host synchronisation in between: a peer
+        # that ran ahead and overwrote a result before it was read would show as a mismatch (identical
+        # inputs would hide it).  Results are read on the calling stream (clone) and on a side stream
+        # that is made a dependency of the calling stream before the next call, as documented.
+        acts = [inputs.gemm_llm(M, K, N, torch.bfloat16, device=dev, seed=50 + i)[0] for i in range(6)]
+        wants = [gemm.gemm(x, w) for x in acts]
+        side = torch.cuda.Stream()
+        same_stream, side_stream = [], []
+        for x in acts:
+            c = fused(x, w[:, s:e])
+            same_stream.append(c.clone())
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                side_stream.append(c.clone())
+            torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        for got1, got2, want in zip(same_stream, side_stream, wants):
+            ok &= torch.equal(got1, want) and torch.equal(got2, want)
+        # the NCCL path in both layouts: column slabs as delivered, and reassembled row-major
+        recv = shard.all_gather_slabs(gemm.gemm(a, w[:, s:e]), slabs)
+        for r, (s0, e0) in enumerate(slabs):
+            ok &= torch.equal(recv[r, :, :e0 - s0], full[:, s0:e0])
         # attention sharded over (batch, kv-head group)
         q, k, v = inputs.fmha_inputs(2, 8, 2, 300, 300, 128, torch.float16, device=dev, seed=9)
         whole = fmha.fmha_fwd(q, k, v, causal=True)

@@ -8,6 +8,8 @@ import torch
 from . import _lib
 
 _DTYPES = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+# query rows per KV head (query heads of the group x Sq) one launch of the split-KV kernel takes
+MAX_DECODE_ROWS = 16
 
 
 def _check_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
@@ -71,9 +73,10 @@ def decode_workspace(B: int, Hq: int, Hkv: int, Sq: int, Skv: int, D: int, num_s
 
 
 def decode_static_fits(B: int, Hq: int, Hkv: int, Sq: int, Skv: int, D: int) -> bool:
-    """Whether the allocation-free decode entry point can take this problem (its unsplit partials
-    must fit the scratch array built into the library)."""
-    return B * Hq * Sq * (D + 2) * 4 <= int(_lib.lib().b200k_fmha_decode_static_scratch_bytes())
+    """Whether the allocation-free decode entry point can take this problem with the split count left
+    to the library: always (the count is lowered until the partials fit the built-in scratch array;
+    one split per sequence keeps no partials)."""
+    return True
 
 
 def fmha_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_lens: torch.Tensor | None = None,
@@ -82,7 +85,9 @@ def fmha_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_lens: torc
     """Split-KV attention for decode-shaped inputs (q [B,Hq,Sq,D] with small Sq, normally 1).
     kv_lens: int32 [B] on the device (valid keys of each sequence) or None for all of Skv.
     static_scratch: use the entry point that keeps its partials in the library's built-in scratch
-    array instead of a workspace tensor (nothing is allocated; for callers inside a graph capture)."""
+    array instead of a workspace tensor, for callers that must not allocate device memory on this path
+    (the first such call on a device looks the array's address up and belongs outside a stream capture;
+    calls that overlap on one GPU race on the shared array)."""
     _check_qkv(q, k, v)
     B, Hq, Sq, D = q.shape
     Hkv, Skv = k.size(1), k.size(2)
@@ -92,6 +97,18 @@ def fmha_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_lens: torc
         return out
     if Skv == 0:
         return out.zero_()
+    group = Hq // Hkv
+    if group * Sq > MAX_DECODE_ROWS and Sq <= MAX_DECODE_ROWS:
+        # More query rows share a KV head than the kernel's 16-row tile holds (MQA, wide GQA groups):
+        # the query heads of every group are taken in slices that fit, each slice one launch over the
+        # same K/V (q and o are a few KB per sequence; K/V are not copied).
+        per = max(g for g in range(1, group + 1) if group % g == 0 and g * Sq <= MAX_DECODE_ROWS)
+        q5, o5 = q.unflatten(1, (Hkv, group)), out.unflatten(1, (Hkv, group))
+        for j in range(0, group, per):
+            part = fmha_decode(q5[:, :, j:j + per].flatten(1, 2), k, v, kv_lens=kv_lens, num_splits=num_splits,
+                               scale=scale, workspace=workspace, static_scratch=static_scratch)
+            o5[:, :, j:j + per].copy_(part.unflatten(1, (Hkv, per)))
+        return out
     q, k, v = _rows_contiguous(q), _rows_contiguous(k), _rows_contiguous(v)
     if kv_lens is not None:
         if kv_lens.dtype != torch.int32 or kv_lens.device != q.device or kv_lens.numel() != B:

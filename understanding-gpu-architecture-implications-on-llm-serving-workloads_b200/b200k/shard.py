@@ -68,13 +68,15 @@ def balance_sequences(kv_lens: Sequence[int], world: int) -> List[List[int]]:
     return out
 
 
-def all_gather_columns(c_local: torch.Tensor, slabs: Sequence[Tuple[int, int]], group=None) -> torch.Tensor:
-    """Reassembles C[M,N] from per-rank column slabs (the one collective of the GEMM path).
-    Slabs may differ in width; they are gathered padded to the widest and trimmed."""
+def all_gather_slabs(c_local: torch.Tensor, slabs: Sequence[Tuple[int, int]], group=None) -> torch.Tensor:
+    """The one collective of the GEMM path: every rank's column slab of C on every rank, as the
+    collective delivers it: a [world, M, widest slab] tensor whose entry r holds C[:, slab_r] in its
+    first (end_r - start_r) columns (narrower slabs are zero-padded).  No reassembly copy: a consumer
+    that can take C as column slabs (the next column-sharded layer, a reduction over rows) reads this
+    directly."""
     world = dist.get_world_size(group)
     M = c_local.size(0)
-    widths = [e - s for (s, e) in slabs]
-    wmax = max(widths)
+    wmax = max(e - s for (s, e) in slabs)
     send = c_local
     if c_local.size(1) != wmax:
         send = c_local.new_zeros((M, wmax))
@@ -82,10 +84,23 @@ def all_gather_columns(c_local: torch.Tensor, slabs: Sequence[Tuple[int, int]], 
     send = send.contiguous()
     recv = send.new_empty((world * M, wmax))  # rank-major concatenation along dim 0
     dist.all_gather_into_tensor(recv, send, group=group)
-    recv = recv.view(world, M, wmax)
-    out = send.new_empty((M, slabs[-1][1]))
-    for r, (s, e) in enumerate(slabs):
-        out[:, s:e] = recv[r, :, :e - s]
+    return recv.view(world, M, wmax)
+
+
+def all_gather_columns(c_local: torch.Tensor, slabs: Sequence[Tuple[int, int]], group=None,
+                       out: torch.Tensor | None = None) -> torch.Tensor:
+    """Reassembles the row-major C[M,N] from per-rank column slabs: all_gather_slabs plus the copy
+    into column windows (one strided copy when all slabs have one width, else one per slab)."""
+    recv = all_gather_slabs(c_local, slabs, group)
+    world, M, wmax = recv.shape
+    N = slabs[-1][1]
+    if out is None:
+        out = recv.new_empty((M, N))
+    if all(e - s == wmax for (s, e) in slabs):
+        out.view(M, world, wmax).copy_(recv.permute(1, 0, 2))
+    else:
+        for r, (s, e) in enumerate(slabs):
+            out[:, s:e] = recv[r, :, :e - s]
     return out
 
 
@@ -132,7 +147,14 @@ class FusedAllGatherGemm:
     its column slab and stores every finished tile into the C buffers of all ranks, which live
     in symmetric (peer-mapped) memory; a symmetric-memory barrier then orders the ranks.  No NCCL
     collective and no multicast load is involved: the data crosses NVLink as plain TMA stores
-    while later tiles are still being computed.  GPU only (needs the library)."""
+    while later tiles are still being computed.  GPU only (needs the library).
+
+    Reuse: two symmetric C buffers alternate from call to call.  The result of call n is this rank's
+    buffer n % 2; peers next write it in call n + 2, and they can only reach that call after this rank
+    has passed the barrier of call n + 1, which sits behind this rank's own work on the calling stream.
+    So a result may be read, ON THE CALLING STREAM, until the call after the next is issued; a
+    consumer on another stream must be made a dependency of the calling stream (wait_stream / event)
+    before call n + 1 is issued."""
 
     def __init__(self, M: int, N: int, dtype, device, group=None):
         import torch.distributed._symmetric_memory as symm_mem
@@ -143,26 +165,36 @@ class FusedAllGatherGemm:
             raise RuntimeError("at most 8 destinations (one node)")
         self.M, self.N = M, N
         self.slabs = gemm_column_slabs(N, self.world)
-        self.c_full = symm_mem.empty((M, N), dtype=dtype, device=device)
-        self.handle = symm_mem.rendezvous(self.c_full, self.group)
-        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.bufs, self.handles, self.ptrs = [], [], []
+        for _ in range(2):
+            buf = symm_mem.empty((M, N), dtype=dtype, device=device)
+            handle = symm_mem.rendezvous(buf, self.group)
+            self.bufs.append(buf)
+            self.handles.append(handle)
+            self.ptrs.append([int(p) for p in handle.buffer_ptrs])
+        self.calls = 0
 
     def __call__(self, a: torch.Tensor, b_slab: torch.Tensor) -> torch.Tensor:
         """a [M,K]; b_slab = this rank's columns of the weight, [K, slab width].  Returns the
-        full C [M,N] (this rank's symmetric buffer), valid on return in stream order."""
+        full C [M,N] (one of this rank's two symmetric buffers), valid on return in stream order."""
         import ctypes
         from . import _lib
         from .gemm import _DTYPES
         s, e = self.slabs[self.rank]
         if b_slab.size(1) != e - s or a.size(0) != self.M or a.size(1) != b_slab.size(0):
             raise RuntimeError("operand shapes do not match this rank's slab")
+        which = self.calls % 2
+        self.calls += 1
         if e > s:
-            esz = self.c_full.element_size()
-            dsts = (ctypes.c_void_p * self.world)(*[p + s * esz for p in self.ptrs])
+            esz = self.bufs[which].element_size()
+            # destinations start with this rank's own buffer and go round the ring, so that at any
+            # moment the ranks' stores head for different GPUs (the kernel also rotates per tile)
+            order = [(self.rank + i) % self.world for i in range(self.world)]
+            dsts = (ctypes.c_void_p * self.world)(*[self.ptrs[which][r] + s * esz for r in order])
             code = _lib.lib().b200k_gemm_scatter(
                 a.data_ptr(), b_slab.data_ptr(), dsts, self.world, self.M, e - s, a.size(1),
                 a.stride(0), b_slab.stride(0), self.N, _DTYPES[a.dtype],
                 _lib.raw_stream(a.device))
             _lib.check(code, "b200k_gemm_scatter")
-        self.handle.barrier()
-        return self.c_full
+        self.handles[which].barrier()
+        return self.bufs[which]

@@ -29,6 +29,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math.h>
+#include <mutex>
 
 #include "host_common.h"
 #include "ptx.cuh"
@@ -820,6 +821,8 @@ static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBy
 int static_scratch_ptr(unsigned char** out) {
   constexpr int kMaxDev = 64;
   static unsigned char* ptrs[kMaxDev] = {};
+  static std::mutex mu;  // the per-device table is filled lazily by whichever host thread comes first
+  std::lock_guard<std::mutex> lock(mu);
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) {
     (void)cudaGetLastError();
@@ -873,10 +876,14 @@ extern "C" int b200k_fmha_decode_splitkv_static(const void* Q, const void* K, co
     splits = choose_splits(B, Hkv, Skv);
     while (splits > 1 && decode_partials_bytes(B, Hq, Hkv, Sq, D, splits) > kStaticScratchBytes) --splits;
   }
-  if (decode_partials_bytes(B, Hq, Hkv, Sq, D, splits) > kStaticScratchBytes) return B200K_ESCRATCH;
+  // One split per sequence keeps no partials at all (the split kernel normalises and writes O itself),
+  // so such a call neither has to fit the array nor needs its address.
   unsigned char* scratch = nullptr;
-  int r = static_scratch_ptr(&scratch);
-  if (r) return r;
+  if (splits > 1) {
+    if (decode_partials_bytes(B, Hq, Hkv, Sq, D, splits) > kStaticScratchBytes) return B200K_ESCRATCH;
+    int r = static_scratch_ptr(&scratch);
+    if (r) return r;
+  }
   const size_t rows = (size_t)B * Hkv * (size_t)(Hq / Hkv * Sq);
   // Nothing has to start at zero: every (max, sum, partial O) slot the reduction kernel
   // reads was written by the split kernel of this same call; slots of splits past a

@@ -116,6 +116,14 @@ __device__ __forceinline__ uint16_t pack1s(float x) {
   }
 }
 template <bool BF16>
+__device__ __forceinline__ float unpack1s(uint16_t u) {
+  if constexpr (BF16) {
+    return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&u));
+  } else {
+    return __half2float(*reinterpret_cast<const __half*>(&u));
+  }
+}
+template <bool BF16>
 __device__ __forceinline__ uint32_t pack2s(float lo, float hi) {
   if constexpr (BF16) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -316,7 +324,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             if (m < M && col < N) {
               if constexpr (EPI == 2) {
                 C[(int64_t)m * ldc + col / 2] = pack1s<BF16>(silu_mul_s(lo, hi));
-              } else {
+              } else if (col + 1 < N) {
                 if constexpr (EPI == 1) {
                   float rl, rh;
                   unpack2s<BF16>(*reinterpret_cast<const uint32_t*>(R + (int64_t)m * ldr + col), rl, rh);
@@ -324,6 +332,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                   hi += rh;
                 }
                 *reinterpret_cast<uint32_t*>(C + (int64_t)m * ldc + col) = pack2s<BF16>(lo, hi);
+              } else {
+                // odd N: the last column alone (a C that is a column window of a wider tensor must not
+                // be written, nor R read, past column N)
+                if constexpr (EPI == 1) lo += unpack1s<BF16>(R[(int64_t)m * ldr + col]);
+                C[(int64_t)m * ldc + col] = pack1s<BF16>(lo);
               }
             }
           }
@@ -398,6 +411,17 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             // columns n..n+3 are (gate, up), (gate, up) of outputs n/2 and n/2+1
             *reinterpret_cast<uint32_t*>(C + (int64_t)row * ldc + n / 2) =
                 pack2s<BF16>(silu_mul_s(acc.x, acc.y), silu_mul_s(acc.z, acc.w));
+          } else if (n + 3 >= N) {
+            // ragged last chunk (N not a multiple of 4): element by element, nothing past column N
+            const float part4[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (n + e < N) {
+                float x = part4[e];
+                if constexpr (EPI == 1) x += unpack1s<BF16>(R[(int64_t)row * ldr + n + e]);
+                C[(int64_t)row * ldc + n + e] = pack1s<BF16>(x);
+              }
+            }
           } else {
             if constexpr (EPI == 1) {
               const uint2 r2 = *reinterpret_cast<const uint2*>(R + (int64_t)row * ldr + n);

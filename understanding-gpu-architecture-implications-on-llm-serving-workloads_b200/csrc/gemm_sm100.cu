@@ -342,7 +342,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0 && row0 < M && col0 < N) {
-            for (int d = 0; d < num_dst; ++d) tma_store_2d(&tmC.m[d], buf, col0, row0);
+            // several destinations (the scatter entry point): the order rotates with the tile and the
+            // chunk, so that the CTAs in flight spread their stores over all destinations' links at
+            // any moment instead of walking them in step (the caller rotates the list per rank too)
+            int d = num_dst > 1 ? (mb + nb + c) % num_dst : 0;
+            for (int i = 0; i < num_dst; ++i) {
+              tma_store_2d(&tmC.m[d], buf, col0, row0);
+              d = d + 1 == num_dst ? 0 : d + 1;
+            }
             tma_store_commit();
           }
         }
@@ -464,12 +471,17 @@ int launch_tc(const void* A, const void* B, void* const* Cs, int num_dst, int M,
     if (r) return r;
   }
   for (int d = 0; d < kMaxDst; ++d) {
+    // only the destinations in use are encoded (one in every call but the scatter entry point);
     // unused slots repeat the first map so that the parameter block holds no garbage
+    if (d >= num_dst) {
+      tmC.m[d] = tmC.m[0];
+      continue;
+    }
     // the SwiGLU epilogue writes N/2 columns, 32 per chunk (64-byte rows, 64-byte swizzle)
     uint64_t dims[2] = {(uint64_t)(EPI == kEpiSwiglu ? N / 2 : N), (uint64_t)M};
     uint64_t str[1] = {(uint64_t)ldc * 2};
     uint32_t box[2] = {EPI == kEpiSwiglu ? 32u : 64u, 32};
-    int r = encode_tmap_16bit(&tmC.m[d], Cs[d < num_dst ? d : 0], 2, dims, str, box, EPI == kEpiSwiglu ? 2 : 1);
+    int r = encode_tmap_16bit(&tmC.m[d], Cs[d], 2, dims, str, box, EPI == kEpiSwiglu ? 2 : 1);
     if (r) return r;
   }
   int* status = status_ptr();
