@@ -49,7 +49,10 @@ enum {
   B200K_GEMM_2CTA = 2,      /* 256x256x64 tiles on a CTA pair (cta_group::2) */
   B200K_GEMM_SKINNY = 3,    /* M <= 128: weight streaming, split-K inside thread-block clusters */
   B200K_GEMM_1CTA_N128 = 4, /* 128x128x64 tiles: more CTAs for small problems */
-  B200K_GEMM_GENERIC = 5    /* CUDA-core kernel without alignment rules (any M, N, K, ld) */
+  B200K_GEMM_GENERIC = 5,   /* CUDA-core kernel without alignment rules (any M, N, K, ld) */
+  B200K_GEMM_2CTA_N128 = 6  /* 256x128x64 tiles on a CTA pair: half-size tiles for problems whose
+                               256x256 tiles would leave most of the last wave of CTA pairs idle
+                               (column slabs of a sharded weight) */
 };
 
 /*
@@ -246,6 +249,28 @@ int b200k_device_supported(void);
  * instruction descriptor: kind::f16, fp32 accumulate, major 0 = K, 1 = MN.
  * The reference has no counterpart (its kernels use WMMA fragments).
  */
+/*
+ * Tuning overrides for experiments and tests; 0 = the library's own choice (the default).
+ * Each option starts from an environment variable of the same name without `OPT_`
+ * (B200K_SKINNY_S, ...), read ONCE when the first launch asks; b200k_set_option changes it
+ * afterwards and returns the previous value (or B200K_EARG).  No launch reads the environment.
+ *   B200K_OPT_SKINNY_S              K-splits (cluster size, 1..8) of the weight-streaming GEMM
+ *   B200K_OPT_SKINNY_BN             its slab width, 128 or 256 columns
+ *   B200K_OPT_DECODE_HEADS_PER_CTA  h >= 1: decode grid of (split, groups of h KV heads, sequence)
+ *   B200K_OPT_FMHA_PERSISTENT       1 = persistent prefill kernel, 2 = one work item per CTA
+ *                                   (the environment variable says 1 / 0)
+ * The reference's counterpart is the set of template parameters fixed in each launcher
+ * (e.g. kernels/gemm/pkg/gemm_unified/csrc/semi/gemm_11_nv.cu:209-213).
+ */
+enum {
+  B200K_OPT_SKINNY_S = 0,
+  B200K_OPT_SKINNY_BN = 1,
+  B200K_OPT_DECODE_HEADS_PER_CTA = 2,
+  B200K_OPT_FMHA_PERSISTENT = 3,
+  B200K_OPT_COUNT = 4
+};
+int b200k_set_option(int which, int value);
+
 /*
  * Failure-path self test: launches one warp that waits at most limit_ns (<= 100 ms)
  * on a barrier nothing arrives on, records B200K_ETIMEOUT in the device status word

@@ -111,6 +111,20 @@ def fmha_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = F
     return out
 
 
+def torch_attn_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool) -> torch.Tensor:
+    """The reference test scripts' own oracle as they compute it (kernels/fmha/test/perf.py:10-24,
+    kernels/fmha/test/correct.py:10-24): every KV head repeated over its group of query heads
+    (expand + reshape) and torch's scaled_dot_product_attention.  The group size is taken from the
+    shapes (the scripts hard-code 4).  This is the function the CPU baseline of the attention paths
+    times; `fmha_ref` is the same math with valid lengths and the bottom-right diagonal added."""
+    if q.size(1) != k.size(1):
+        n_rep = q.size(1) // k.size(1)
+        b, h, s, d = k.shape
+        k = k[:, :, None, :, :].expand(b, h, n_rep, s, d).reshape(b, h * n_rep, s, d)
+        v = v[:, :, None, :, :].expand(b, h, n_rep, s, d).reshape(b, h * n_rep, s, d)
+    return torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=is_causal)
+
+
 def fmha_ref_online(q: np.ndarray, k: np.ndarray, v: np.ndarray, causal: bool = False, kv_len: int | None = None,
                     block: int = 64) -> np.ndarray:
     """Blocked online-softmax recurrences of the reference kernels in fp32 numpy
@@ -169,23 +183,33 @@ def bf16_ulp(ref: torch.Tensor) -> torch.Tensor:
     return torch.exp2(torch.floor(torch.log2(mag)) - 7)
 
 
-def fmha_within_tolerance(o: torch.Tensor, ref: torch.Tensor, extra: float = 0.0) -> tuple[bool, float]:
+def fmha_within_tolerance(o: torch.Tensor, ref: torch.Tensor, extra: float = 0.0,
+                          absref: torch.Tensor | None = None) -> tuple[bool, float]:
     """The attention bar, returned as (ok, worst max-abs error).
 
     fp16 output: max-abs <= FMHA_MAX_ABS_TOL against the fp32 formula, as stated.
     bf16 output: a bf16 number cannot sit within 2e-3 of an fp32 value above ~0.5 (its spacing
-    there is 2^-8 and up), so the unavoidable output rounding is stated separately from the
-    kernel's own error: against the fp32 formula ROUNDED TO bf16 every element must lie within
-    FMHA_MAX_ABS_TOL plus one bf16 spacing at that element, and against the unrounded formula
-    within FMHA_MAX_ABS_TOL + 2^-8 max|ref| overall."""
+    there is 2^-8 and up), and the probabilities P enter the second product as bf16 (8 significant
+    bits, relative rounding error up to 2^-9 each).  So the unavoidable part is stated separately from
+    the kernel's own error, three ways:
+      * overall, against the unrounded formula: max-abs <= FMHA_MAX_ABS_TOL + 2^-8 max|ref|;
+      * on average: relative Frobenius error <= 3e-3 (output rounding alone gives about 1.6e-3; a
+        systematic 2^-8 error anywhere in the arithmetic would give 4e-3 or more);
+      * per element, when `absref` = softmax(QK^T) |V| is given (the formula evaluated on |V|, which
+        bounds how far rounding P can move each output): |o - bf16(ref)| <= FMHA_MAX_ABS_TOL + one bf16
+        spacing at ref + 2^-8 absref, so an error cannot hide behind the largest output of the tensor."""
     o64, r64 = o.detach().cpu().double(), ref.detach().cpu().double()
     err = float((o64 - r64).abs().max())
     if o.dtype != torch.bfloat16:
         return err <= FMHA_MAX_ABS_TOL + extra, err
-    rounded = ref.detach().cpu().float().to(torch.bfloat16).double()
-    elementwise = bool(((o64 - rounded).abs() <= FMHA_MAX_ABS_TOL + extra + bf16_ulp(ref)).all())
-    overall = err <= FMHA_MAX_ABS_TOL + extra + float(r64.abs().max()) * 2.0 ** -8
-    return elementwise and overall, err
+    ok = err <= FMHA_MAX_ABS_TOL + extra + float(r64.abs().max()) * 2.0 ** -8
+    den = float(torch.linalg.norm(r64))
+    ok = ok and (den == 0.0 or float(torch.linalg.norm(o64 - r64)) / den <= 3e-3)
+    if absref is not None:
+        rounded = ref.detach().cpu().float().to(torch.bfloat16).double()
+        bound = FMHA_MAX_ABS_TOL + extra + bf16_ulp(ref) + absref.detach().cpu().double().abs() * 2.0 ** -8
+        ok = ok and bool(((o64 - rounded).abs() <= bound).all())
+    return ok, err
 
 
 GEMM_REL_FRO_TOL = 1e-2   # stated tolerance: relative Frobenius error vs fp32 matmul

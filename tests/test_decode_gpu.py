@@ -28,7 +28,8 @@ def test_parity_uniform_length(cuda_device, Skv, D, dtype):
     o = _decode(q, k, v, None, cuda_device)
     ref = oracle.fmha_ref(q, k, v)
     # fp16: 2e-3 max-abs; bf16: 2e-3 + one bf16 spacing around the formula rounded to bf16, element-wise
-    ok, err = oracle.fmha_within_tolerance(o, ref)
+    absref = oracle.fmha_ref(q, k, v.abs()) if dtype == torch.bfloat16 else None
+    ok, err = oracle.fmha_within_tolerance(o, ref, absref=absref)
     assert ok, err
 
 
@@ -196,8 +197,8 @@ def test_paged_cache_matches_dense(cuda_device, page_size):
 
 @pytest.mark.parametrize("D,dtype", [(128, torch.float16), (64, torch.bfloat16)])
 @pytest.mark.parametrize("Hq,Hkv,splits", [(24, 6, 1), (8, 8, 1), (32, 8, 3)])
-def test_heads_grouped_per_cta_bit_identical(cuda_device, monkeypatch, Hq, Hkv, splits, D, dtype):
-    """A CTA may walk several KV heads of its sequence (B200K_DECODE_HEADS_PER_CTA forces the
+def test_heads_grouped_per_cta_bit_identical(cuda_device, Hq, Hkv, splits, D, dtype):
+    """A CTA may walk several KV heads of its sequence (B200K_OPT_DECODE_HEADS_PER_CTA forces the
     group size; the library's own work lists are covered by the single-split test below).  Every
     grouping - including one that does not divide the head count and one larger than it - gives
     the bits of one head per CTA, with ragged lengths, an empty sequence and NaN padding."""
@@ -208,19 +209,21 @@ def test_heads_grouped_per_cta_bit_identical(cuda_device, monkeypatch, Hq, Hkv, 
     for b in range(B):
         k[b, :, int(lens[b]):] = float("nan")
         v[b, :, int(lens[b]):] = float("nan")
-    monkeypatch.setenv("B200K_DECODE_HEADS_PER_CTA", "1")
-    base = _decode(q, k, v, lens, cuda_device, num_splits=splits)
+    from b200k import _lib
+    with _lib.option(_lib.OPT_DECODE_HEADS_PER_CTA, 1):
+        base = _decode(q, k, v, lens, cuda_device, num_splits=splits)
     ref = oracle.fmha_ref(q, k, v, kv_lens=lens)
-    ok, err = oracle.fmha_within_tolerance(base, ref)
+    absref = oracle.fmha_ref(q, k, v.abs(), kv_lens=lens) if dtype == torch.bfloat16 else None
+    ok, err = oracle.fmha_within_tolerance(base, ref, absref=absref)
     assert ok, err
     assert torch.equal(base[1], torch.zeros_like(base[1]))
     for h in (2, 4, 16):
-        monkeypatch.setenv("B200K_DECODE_HEADS_PER_CTA", str(h))
-        o = _decode(q, k, v, lens, cuda_device, num_splits=splits)
+        with _lib.option(_lib.OPT_DECODE_HEADS_PER_CTA, h):
+            o = _decode(q, k, v, lens, cuda_device, num_splits=splits)
         assert torch.equal(o.view(torch.int16), base.view(torch.int16)), h
 
 
-def test_single_split_writes_output_directly(cuda_device, monkeypatch):
+def test_single_split_writes_output_directly(cuda_device):
     """With one split per sequence the split kernel normalises and writes O itself (one launch,
     no partials), and with more (sequence, head) pairs than SMs its CTAs walk strided lists of
     pairs.  The result has the bits of one CTA per pair, also through a strided, 2-byte-aligned
@@ -245,8 +248,8 @@ def test_single_split_writes_output_directly(cuda_device, monkeypatch):
     assert oracle.max_abs(o2.cpu(), ref) <= TOL
     assert torch.equal(o3, o1)
     assert torch.all(big[..., 0] == 7.0) and torch.all(big[..., D + 1] == 7.0)
-    monkeypatch.setenv("B200K_DECODE_HEADS_PER_CTA", "1")
-    o4 = fmha.fmha_decode(qd, kd, vd, kv_lens=ld, num_splits=1)
+    with _lib.option(_lib.OPT_DECODE_HEADS_PER_CTA, 1):
+        o4 = fmha.fmha_decode(qd, kd, vd, kv_lens=ld, num_splits=1)
     torch.cuda.synchronize()
     assert torch.equal(o4, o1)
     assert torch.equal(o1[0], torch.zeros_like(o1[0])) and torch.equal(o1[B - 1], torch.zeros_like(o1[0]))

@@ -13,6 +13,21 @@ pytestmark = pytest.mark.gpu
 TOL = oracle.GEMM_REL_FRO_TOL
 
 
+@pytest.fixture
+def skinny_splits():
+    """Forces the K-split count (cluster size) of the weight-streaming GEMM for one test through the
+    library's tuning override and puts the library's own choice back afterwards."""
+    from b200k import _lib
+    before = []
+
+    def force(splits: int):
+        before.append(_lib.lib().b200k_set_option(_lib.OPT_SKINNY_S, int(splits)))
+
+    yield force
+    if before:
+        _lib.lib().b200k_set_option(_lib.OPT_SKINNY_S, before[0])
+
+
 def _run(a, b, variant, dev):
     from b200k import gemm
     c = gemm.gemm(a.to(dev), b.to(dev), variant=variant)
@@ -152,12 +167,12 @@ def test_skinny_split_k_clusters(cuda_device, shape, dtype):
 @pytest.mark.parametrize("splits", [1, 2, 5, 8])
 @pytest.mark.parametrize("shape", [(1, 136, 192), (7, 264, 200), (16, 512, 1024), (33, 1096, 520), (64, 2048, 512),
                                    (100, 520, 264), (128, 384, 640)])
-def test_skinny_cluster_sizes_and_epilogues(cuda_device, monkeypatch, shape, splits, dtype):
+def test_skinny_cluster_sizes_and_epilogues(cuda_device, skinny_splits, shape, splits, dtype):
     """Every cluster size the heuristic can pick, forced through the documented override, with all
     three epilogues: a cluster of one stores C straight from the accumulators (odd row counts, ragged
     N), larger ones reduce through distributed shared memory (uneven column shares at 5 and 8)."""
     from b200k import gemm
-    monkeypatch.setenv("B200K_SKINNY_S", str(splits))
+    skinny_splits(splits)
     M, N, K = shape
     a, b = _inputs(M, N, K, dtype, seed=M + N + K + splits, std_b=0.1)
     ad, bd = a.to(cuda_device), b.to(cuda_device)
@@ -174,13 +189,12 @@ def test_skinny_cluster_sizes_and_epilogues(cuda_device, monkeypatch, shape, spl
 
 @pytest.mark.parametrize("splits", [0, 1, 3])
 @pytest.mark.parametrize("M", [5, 64, 128])
-def test_skinny_strided_operands(cuda_device, monkeypatch, M, splits):
+def test_skinny_strided_operands(cuda_device, skinny_splits, M, splits):
     """Row-strided A, B and C (views into wider tensors, as the column-slab sharding produces them): the
     weight-streaming kernel honours all three leading dimensions on its direct-store, push and pull
     paths, and leaves the columns outside the output view untouched."""
     from b200k import gemm
-    if splits:
-        monkeypatch.setenv("B200K_SKINNY_S", str(splits))
+    skinny_splits(splits)
     K, N = 520, 392
     g = torch.Generator().manual_seed(M + splits)
     a_big = torch.randn(M, K + 24, generator=g).to(torch.bfloat16).to(cuda_device)
@@ -196,12 +210,12 @@ def test_skinny_strided_operands(cuda_device, monkeypatch, M, splits):
 @pytest.mark.parametrize("splits", [1, 3])
 @pytest.mark.parametrize("N", [130, 134, 263, 517])
 @pytest.mark.parametrize("M", [3, 64, 128])
-def test_skinny_column_window_ragged_n(cuda_device, monkeypatch, M, N, splits):
+def test_skinny_column_window_ragged_n(cuda_device, skinny_splits, M, N, splits):
     """C (and the residual R) as the first N columns of a wider tensor with N not a multiple of 4 (nor
     of 2): the weight-streaming kernel's 4-wide (split-K) and 2-wide (single CTA) stores must stop at
     column N, and the fused add must not read R beyond it."""
     from b200k import gemm
-    monkeypatch.setenv("B200K_SKINNY_S", str(splits))
+    skinny_splits(splits)
     K = 264
     a, b = _inputs(M, N, K, torch.bfloat16, seed=M + N, std_b=0.1)
     wide = (N + 15) // 8 * 8 + 8

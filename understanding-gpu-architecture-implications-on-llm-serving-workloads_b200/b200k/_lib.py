@@ -46,6 +46,7 @@ SIGNATURES = {
     "b200k_device_status": (c_int, [POINTER(c_int), POINTER(c_int)]),
     "b200k_launch_count": (c_uint64, []),
     "b200k_device_supported": (c_int, []),
+    "b200k_set_option": (c_int, [c_int, c_int]),
     "b200k_debug_wait_timeout": (c_int, [c_uint64, c_void_p]),
     "b200k_debug_smem_desc": (c_uint64, [ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32]),
     "b200k_debug_instr_desc": (ctypes.c_uint32, [c_int, c_int, c_int, c_int, c_int]),
@@ -87,6 +88,27 @@ def strerror(code: int) -> str:
 def check(code: int, where: str) -> None:
     if code != 0:
         raise B200KError(code, where)
+
+
+OPT_SKINNY_S, OPT_SKINNY_BN, OPT_DECODE_HEADS_PER_CTA, OPT_FMHA_PERSISTENT = 0, 1, 2, 3
+
+
+class option:
+    """`with option(OPT_SKINNY_S, 4): ...` sets a tuning override of the library (b200k_set_option)
+    for the block and restores the previous value afterwards."""
+
+    def __init__(self, which: int, value: int):
+        self.which, self.value = which, value
+
+    def __enter__(self):
+        self.before = lib().b200k_set_option(self.which, self.value)
+        if self.before < 0:
+            raise B200KError(self.before, "b200k_set_option")
+        return self
+
+    def __exit__(self, *exc):
+        lib().b200k_set_option(self.which, self.before)
+        return False
 
 
 def launch_count() -> int:

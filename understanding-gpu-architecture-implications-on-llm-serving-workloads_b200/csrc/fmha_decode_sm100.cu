@@ -610,13 +610,12 @@ int item_stride_of(int B, int Hkv, int splits) {
   return (int)((pairs + per_cta - 1) / per_cta);
 }
 
-// Override for experiments and tests, read at every call: B200K_DECODE_HEADS_PER_CTA = h >= 1 gives the
-// grid (split, groups of h consecutive KV heads, sequence) instead, also with split sequences.
+// Override for experiments and tests (B200K_OPT_DECODE_HEADS_PER_CTA): h >= 1 gives the grid
+// (split, groups of h consecutive KV heads, sequence) instead, also with split sequences.
 int heads_per_cta_override(int Hkv) {
-  const char* e = getenv("B200K_DECODE_HEADS_PER_CTA");
-  const int env = e ? atoi(e) : 0;
-  if (env < 1) return 0;
-  return env < Hkv ? env : Hkv;
+  const int h = tuning_option(B200K_OPT_DECODE_HEADS_PER_CTA);
+  if (h < 1) return 0;
+  return h < Hkv ? h : Hkv;
 }
 
 int chunk_of(int Skv, int splits) {

@@ -1122,12 +1122,9 @@ extern "C" int b200k_fmha_fwd(const void* Q, const void* K, const void* V, void*
   // Default: the persistent kernel for kv_len <= 4096 (measured +3 % at 4096, +10 % at 2048, +19..31 %
   // at 1024, where per-CTA set-up weighs most), the one-item-per-CTA kernel beyond (measured 5-7 %
   // ahead at 8192 / 16384, where the hardware's dynamic CTA scheduling balances better than the static
-  // item lists).  B200K_FMHA_PERSISTENT=0/1 overrides.
-  static const int env_persistent = [] {
-    const char* e = getenv("B200K_FMHA_PERSISTENT");
-    return e ? (e[0] == '1' ? 1 : 0) : -1;
-  }();
-  const bool persistent = variant != 0 ? variant >= 10 : env_persistent >= 0 ? env_persistent == 1 : kv_len <= 4096;
+  // item lists).  B200K_OPT_FMHA_PERSISTENT overrides.
+  const int forced = tuning_option(B200K_OPT_FMHA_PERSISTENT);  // 0 library's choice, 1 persistent, 2 one item per CTA
+  const bool persistent = variant != 0 ? variant >= 10 : forced ? forced == 1 : kv_len <= 4096;
   static const int kEmuOfCode[5] = {0, 2, 4, 1, 3};
   const int code = (variant % 10) - 1;
   if (variant != 0 && (code < 0 || code > 4 || variant >= 20)) return B200K_EARG;

@@ -465,13 +465,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 // large and fewer K-splits are needed for the same number of CTAs; beyond one wave of 128-column
 // slabs the 256-column slab is used.  The rate peaks with 96..128 CTAs (more splits add reduction work
 // faster than bytes in flight; more CTAs than SMs means a second wave), so S = round(112 / slabs)
-// for 128-column slabs, round(96 / slabs) for 256-column ones, at most 8, never more CTAs than SMs.  B200K_SKINNY_BN / B200K_SKINNY_S override both.
+// for 128-column slabs, round(96 / slabs) for 256-column ones, at most 8, never more CTAs than SMs.  B200K_OPT_SKINNY_BN / B200K_OPT_SKINNY_S override both.
 int skinny_slab_width(int N) {
-  static const int env_bn = [] {
-    const char* e = getenv("B200K_SKINNY_BN");
-    return e ? atoi(e) : 0;
-  }();
-  if (env_bn == 128 || env_bn == 256) return env_bn;
+  const int forced_bn = tuning_option(B200K_OPT_SKINNY_BN);
+  if (forced_bn == 128 || forced_bn == 256) return forced_bn;
   const int sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
   return (N + 127) / 128 <= sms ? 128 : 256;
 }
@@ -485,10 +482,8 @@ int skinny_cluster_size(int N, int K, int bn) {
   while (s > 1 && s * tiles > sms) --s;
   if (s > num_kb / 2) s = num_kb / 2;
   if (s < 1) s = 1;
-  if (const char* e = getenv("B200K_SKINNY_S")) {
-    const int v = atoi(e);
-    if (v >= 1 && v <= 8 && v <= num_kb) s = v;
-  }
+  const int v = tuning_option(B200K_OPT_SKINNY_S);
+  if (v >= 1 && v <= 8 && v <= num_kb) s = v;
   return s;
 }
 
@@ -553,7 +548,7 @@ int launch_skinny(const void* A, const void* B, void* C, int M, int N, int K, in
                   bool bf16, cudaStream_t stream, int epilogue, const void* R, int64_t ldr) {
   if (M > 128 || epilogue < 0 || epilogue > 2) return B200K_ESHAPE;
   // tiny M on a wide weight: the epilogue is negligible and 512-byte rows stream a little better
-  const bool narrow = skinny_slab_width(N) == 128 && !(M <= 32 && (N + 127) / 128 > 64 && !getenv("B200K_SKINNY_BN"));
+  const bool narrow = skinny_slab_width(N) == 128 && !(M <= 32 && (N + 127) / 128 > 64 && !tuning_option(B200K_OPT_SKINNY_BN));
 #define B200K_SKINNY_B(MP, EP, BNN)                                                                      \
   (bf16 ? launch_skinny_t<MP, true, EP, BNN>(A, B, C, M, N, K, lda, ldb, ldc, stream, R, ldr)            \
         : launch_skinny_t<MP, false, EP, BNN>(A, B, C, M, N, K, lda, ldb, ldc, stream, R, ldr))

@@ -576,6 +576,10 @@ extern "C" int b200k_gemm(const void* A, const void* B, void* C, int M, int N, i
       if (!tma_ok) return B200K_EALIGN;
       return bf16 ? launch_tc<2, 256, 6, true>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream)
                   : launch_tc<2, 256, 6, false>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream);
+    case B200K_GEMM_2CTA_N128:
+      if (!tma_ok) return B200K_EALIGN;
+      return bf16 ? launch_tc<2, 128, 8, true>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream)
+                  : launch_tc<2, 128, 8, false>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream);
     case B200K_GEMM_1CTA_N128:
       if (!tma_ok) return B200K_EALIGN;
       return bf16 ? launch_tc<1, 128, 6, true>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream)

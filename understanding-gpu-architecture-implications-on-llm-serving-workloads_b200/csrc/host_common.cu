@@ -3,6 +3,7 @@
 #include "ptx.cuh"
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 
 namespace b200k {
@@ -135,6 +136,29 @@ int* status_ptr() {
   return ptrs[dev];
 }
 
+namespace {
+std::atomic<int> g_options[B200K_OPT_COUNT];
+std::once_flag g_options_once;
+void read_options_from_env() {
+  static const char* const names[B200K_OPT_COUNT] = {"B200K_SKINNY_S", "B200K_SKINNY_BN", "B200K_DECODE_HEADS_PER_CTA",
+                                                     "B200K_FMHA_PERSISTENT"};
+  for (int i = 0; i < B200K_OPT_COUNT; ++i) {
+    const char* e = getenv(names[i]);
+    int v = e ? atoi(e) : 0;
+    // B200K_FMHA_PERSISTENT keeps its historical meaning in the environment (0 = off, 1 = on);
+    // the option's values are 0 = library's choice, 1 = persistent kernel, 2 = one item per CTA
+    if (i == B200K_OPT_FMHA_PERSISTENT) v = e ? (e[0] == '1' ? 1 : 2) : 0;
+    g_options[i].store(v, std::memory_order_relaxed);
+  }
+}
+}  // namespace
+
+int tuning_option(int which) {
+  if (which < 0 || which >= B200K_OPT_COUNT) return 0;
+  std::call_once(g_options_once, read_options_from_env);
+  return g_options[which].load(std::memory_order_relaxed);
+}
+
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
 int check_launch() {
@@ -189,6 +213,13 @@ int b200k_debug_wait_timeout(uint64_t limit_ns, b200k_stream_t stream) {
   b200k::wait_probe_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(limit_ns, status);
   b200k::count_launch();
   return b200k::check_launch();
+}
+
+int b200k_set_option(int which, int value) {
+  if (which < 0 || which >= B200K_OPT_COUNT || value < 0) return B200K_EARG;
+  const int before = b200k::tuning_option(which);  // makes sure the environment has been read first
+  b200k::g_options[which].store(value, std::memory_order_relaxed);
+  return before;
 }
 
 const char* b200k_strerror(int code) {

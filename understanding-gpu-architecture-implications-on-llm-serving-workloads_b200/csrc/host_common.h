@@ -38,6 +38,11 @@ const DevInfo& dev_info();
 int launch_skinny(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                   bool bf16, cudaStream_t stream, int epilogue = 0, const void* R = nullptr, int64_t ldr = 0);
 
+// Tuning overrides for experiments and tests (B200K_OPT_* in b200k.h).  Each starts from its
+// environment variable, read ONCE when the first launcher asks, and can be changed afterwards with
+// b200k_set_option; 0 = the library's own choice.  A launch reads an atomic, never the environment.
+int tuning_option(int which);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace b200k
