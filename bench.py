@@ -618,6 +618,22 @@ def _extra_skinny(env, extra):
     del graph
 
 
+def _extra_host_path(env, extra):
+    """The smallest configuration (fp16 1024^3, 64 tiles, a few microseconds of device time) through
+    the reference-facing op, one call at a time: what a call costs on the host, next to torch.matmul
+    (cuBLAS through torch's own dispatcher) on the same operands."""
+    from b200k import inputs
+    import gemm_unified
+    a1, b1 = inputs.gemm_c1(env.dev)
+    n = 2000
+    rec = {"workload": "gemm_fp16_1024x1024x1024 (one call at a time)", "binding": gemm_unified._C.BINDING}
+    for name, fn in (("fine_gemm", lambda: gemm_unified.ops.fine_gemm(a1, b1, 12)),
+                     ("torch_matmul", lambda: torch.matmul(a1, b1))):
+        secs = min(time_cuda(fn, n, 20) for _ in range(3))
+        rec[name] = {"us_per_call": secs / n * 1e6, "tflops": 2.0 * 1024 ** 3 * n / secs / 1e12}
+    extra["host_path"] = rec
+
+
 def _extra_sustained(env, extra, a, w, c, sampler):
     """The headline GEMM under sustained load: about 2 s of launches in eight chunks alternating with
     torch.matmul (cuBLAS) on the same operands, so both run at the clocks the 1 kW power cap allows;
@@ -838,6 +854,11 @@ def run_ours(args):
             extra["gemm_allgather_strong"] = {"error": repr(exc)[:300]}
     extra["sharded_bitexact"] = env.all_true(all(exact.values()))
     extra["sharded_bitexact_checks"] = sorted(exact)
+    if world == 1:
+        try:
+            _extra_host_path(env, extra)
+        except Exception as exc:
+            extra["host_path"] = {"error": repr(exc)[:300]}
     if world == 1 and not args.no_sustained:
         try:
             sampler2 = ClockSampler(env.local_rank, period_s=0.005)

@@ -270,6 +270,31 @@ def test_linearity_full_size(cuda_device):
     assert oracle.rel_frobenius(c[rows], ref) <= TOL
 
 
+@pytest.mark.parametrize("N", [1408, 5504, 1472, 1288])
+def test_large_m_partly_filled_last_tile(cuda_device, N):
+    """M = 8192, K = 4096 against column slabs whose last tile is half full or less (1408 = 5.5 tiles of
+    256 columns and 5504 = 21.5 are the slabs of the 4096x11008 weight on 8 and 2 GPUs; 1472 = 11.5 tiles
+    of 128; 1288 leaves 8 columns): chunks of the last tile that lie outside C store nothing, and the
+    epilogue's two staging buffers must still not be overwritten while an earlier store reads them - a
+    race that only shows on a GEMM large enough to keep the stores in flight.  Every element is
+    checked against the fp32 CPU product, and all tensor-core variants agree to the bit."""
+    from b200k import gemm, inputs
+    M, K = 8192, 4096
+    a = inputs.device_randn16((M, K), 700 + N, 1.0, torch.bfloat16, cuda_device)
+    w = inputs.device_randn16((K, 11008), 800 + N, 0.02, torch.bfloat16, cuda_device)
+    ws = w[:, 2816:2816 + N]          # a view into the wider weight, as the sharding produces it
+    ref = oracle.gemm_ref(a.cpu(), ws.cpu())
+    first = None
+    for variant in (0, 2, 1, 4, 6):
+        for rep in range(2):
+            c = gemm.gemm(a, ws, variant=variant)
+            host = c.cpu().float()
+            assert torch.allclose(host, ref, rtol=2.0 ** -7, atol=1e-2), (variant, rep, float((host - ref).abs().max()))
+            if first is None:
+                first = c
+            assert torch.equal(c, first), (variant, rep)
+
+
 def test_error_codes(cuda_device):
     from b200k import gemm
     a = torch.zeros(8, 8, dtype=torch.float16, device=cuda_device)

@@ -82,6 +82,49 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+SHIM_SRC = PKG_DIR / "torch_shim" / "ops_shim.cpp"
+SHIM_PATH = PKG_DIR / "lib" / "libb200k_torch_ops.so"
+
+
+def build_shim(force: bool = False) -> Path:
+    """Compiles the torch-op binding (torch_shim/ops_shim.cpp: the reference's TORCH_LIBRARY schema
+    blocks with CUDA implementations that forward to the C ABI) against the installed torch headers and
+    links it to lib/libb200k.so.  Host C++ only (g++); about a minute because of the torch headers."""
+    import torch
+    from torch.utils import cpp_extension as ce
+    deps = [SHIM_SRC, PKG_DIR.parent / "include" / "b200k.h", LIB_PATH]
+    if not force and not _stale(SHIM_PATH, deps):
+        return SHIM_PATH
+    cuda_home = Path(_nvcc()).resolve().parent.parent
+    torch_lib = Path(torch.__file__).resolve().parent / "lib"
+    flags = ["-O2", "-std=c++17", "-fPIC", "-shared", "-w",
+             f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
+    flags += [f"-I{p}" for p in ce.include_paths()] + [f"-I{cuda_home / 'include'}"]
+    flags += [str(SHIM_SRC), "-o", str(SHIM_PATH)]
+    flags += [f"-L{torch_lib}", "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda",
+              f"-L{LIB_PATH.parent}", "-lb200k", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}"]
+    # The binding throws c10::Error through torch's frames, so it must share torch's C++ runtime
+    # (libstdc++.so.6): a compiler set up to link libstdc++ statically gives a library that loads and
+    # runs until the first exception crosses into torch, and then crashes.  The system g++ is tried
+    # first, $CXX last, and a result without a dynamic libstdc++ is rejected.
+    tried = []
+    for cxx in dict.fromkeys(c for c in (os.environ.get("B200K_CXX"), "/usr/bin/g++", shutil.which("g++"),
+                                          os.environ.get("CXX")) if c and Path(c).exists()):
+        p = subprocess.run([cxx, *flags], capture_output=True, text=True)
+        if p.returncode != 0:
+            tried.append(f"{cxx}: {(p.stdout + p.stderr)[-400:]}")
+            continue
+        with open(SHIM_PATH, "rb") as f:
+            if b"libstdc++.so.6" in f.read():
+                return SHIM_PATH
+        tried.append(f"{cxx}: links libstdc++ statically")
+        SHIM_PATH.unlink()
+    sys.stderr.write("\n".join(tried) + "\n")
+    raise RuntimeError("build of libb200k_torch_ops.so failed")
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(path)
+    if "--no-shim" not in sys.argv:
+        print(build_shim(force="--force" in sys.argv))

@@ -315,8 +315,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0 && row0 < M && col0 < N) {
-            for (int d = 0; d < num_dst; ++d) tma_store_2d(&tmC.m[d], buf, col0 / 2, row0);
+          // One bulk group per chunk, ALSO for a chunk that lies outside C and stores nothing (an empty
+          // group): `tma_store_wait_read<1>` above relies on chunk c - 2, the last user of this staging
+          // buffer, being two groups back.  Without the empty groups a tile with two or more trailing
+          // chunks outside C let a later chunk overwrite a buffer a pending store was still reading.
+          if (lane == 0) {
+            if (row0 < M && col0 < N)
+              for (int d = 0; d < num_dst; ++d) tma_store_2d(&tmC.m[d], buf, col0 / 2, row0);
             tma_store_commit();
           }
         } else {
@@ -341,16 +346,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0 && row0 < M && col0 < N) {
-            // several destinations (the scatter entry point): the order rotates with the tile and the
-            // chunk, so that the CTAs in flight spread their stores over all destinations' links at
-            // any moment instead of walking them in step (the caller rotates the list per rank too)
-            int d = num_dst > 1 ? (mb + nb + c) % num_dst : 0;
-            for (int i = 0; i < num_dst; ++i) {
-              tma_store_2d(&tmC.m[d], buf, col0, row0);
-              d = d + 1 == num_dst ? 0 : d + 1;
+          if (lane == 0) {
+            if (row0 < M && col0 < N) {
+              // several destinations (the scatter entry point): the order rotates with the tile and the
+              // chunk, so that the CTAs in flight spread their stores over all destinations' links at
+              // any moment instead of walking them in step (the caller rotates the list per rank too)
+              int d = num_dst > 1 ? (mb + nb + c) % num_dst : 0;
+              for (int i = 0; i < num_dst; ++i) {
+                tma_store_2d(&tmC.m[d], buf, col0, row0);
+                d = d + 1 == num_dst ? 0 : d + 1;
+              }
             }
-            tma_store_commit();
+            tma_store_commit();  // always: see the SwiGLU branch above (empty groups keep the count in step)
           }
         }
       }

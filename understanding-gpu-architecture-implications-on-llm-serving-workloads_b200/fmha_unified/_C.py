@@ -15,6 +15,9 @@ describes padding the reference's Python wrapper added and is applied as the
 valid key count as well.  Every index accepts fp16 and bf16 and d in {64, 128}.
 One op is added, `finefmha_decode_varlen(q, k, v, kv_lens)`, because a scalar
 `decode_length` cannot carry per-sequence KV lengths.
+
+The registration itself lives in C++ when the compiled binding has been built
+(torch_shim/ops_shim.cpp, loaded here), otherwise in this module over ctypes; see b200k/_binding.py.
 """
 import os
 import sys
@@ -22,18 +25,14 @@ import sys
 import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-from b200k import fmha as _fmha  # noqa: E402
+from b200k import _binding, fmha as _fmha  # noqa: E402
 
 NUM_DECLARED = 8
 NUM_IMPLEMENTED = 6
 # decode-shaped calls (few query rows) go to the split-KV kernels
 DECODE_MAX_SQ = 8
 
-_library = torch.library.Library("fmha_unified", "DEF")
-for _i in range(NUM_DECLARED):
-    _library.define(f"finefmha_{_i}(Tensor q, Tensor k, Tensor v, bool causal, bool is_decode, "
-                    "int decode_length) -> Tensor")
-_library.define("finefmha_decode_varlen(Tensor q, Tensor k, Tensor v, Tensor kv_lens) -> Tensor")
+BINDING = _binding.binding()  # "compiled": the C++ TORCH_LIBRARY blocks are loaded and nothing is defined here
 
 
 def _finefmha(q, k, v, causal: bool, is_decode: bool, decode_length: int):
@@ -54,6 +53,12 @@ def _finefmha_decode_varlen(q, k, v, kv_lens):
     return _fmha.fmha_decode(q, k, v, kv_lens=kv_lens)
 
 
-for _i in range(NUM_IMPLEMENTED):
-    _library.impl(f"finefmha_{_i}", _finefmha, "CUDA")
-_library.impl("finefmha_decode_varlen", _finefmha_decode_varlen, "CUDA")
+if BINDING == "ctypes":
+    _library = torch.library.Library("fmha_unified", "DEF")
+    for _i in range(NUM_DECLARED):
+        _library.define(f"finefmha_{_i}(Tensor q, Tensor k, Tensor v, bool causal, bool is_decode, "
+                        "int decode_length) -> Tensor")
+    _library.define("finefmha_decode_varlen(Tensor q, Tensor k, Tensor v, Tensor kv_lens) -> Tensor")
+    for _i in range(NUM_IMPLEMENTED):
+        _library.impl(f"finefmha_{_i}", _finefmha, "CUDA")
+    _library.impl("finefmha_decode_varlen", _finefmha_decode_varlen, "CUDA")
