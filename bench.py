@@ -54,7 +54,7 @@ FLOPS_PER_STEP = 2.0 * M * N * K
 REFERENCE_SAMPLE_ROWS = 2048
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the GEMM kernel on this
 # workload, from the ncu capture summarised in profiles/
-NCU_TRAFFIC_BYTES = 697283072  # 526.9 MB read + 170.4 MB written
+NCU_TRAFFIC_BYTES = 534907904  # 369.1 MB read + 165.8 MB written
 
 
 def bench_config(n_gpus: int) -> dict:

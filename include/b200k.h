@@ -259,6 +259,9 @@ int b200k_device_supported(void);
  *   B200K_OPT_DECODE_HEADS_PER_CTA  h >= 1: decode grid of (split, groups of h KV heads, sequence)
  *   B200K_OPT_FMHA_PERSISTENT       1 = persistent prefill kernel, 2 = one work item per CTA
  *                                   (the environment variable says 1 / 0)
+ *   B200K_OPT_FMHA_SPLIT_P          head_dim 64: 1 = P goes to TMEM columns of its own, so that the next
+ *                                   block's QK^T is issued ahead of this block's PV product (measured
+ *                                   no faster than P over its S columns, the default)
  * The reference's counterpart is the set of template parameters fixed in each launcher
  * (e.g. kernels/gemm/pkg/gemm_unified/csrc/semi/gemm_11_nv.cu:209-213).
  */
@@ -267,7 +270,8 @@ enum {
   B200K_OPT_SKINNY_BN = 1,
   B200K_OPT_DECODE_HEADS_PER_CTA = 2,
   B200K_OPT_FMHA_PERSISTENT = 3,
-  B200K_OPT_COUNT = 4
+  B200K_OPT_FMHA_SPLIT_P = 4,
+  B200K_OPT_COUNT = 5
 };
 int b200k_set_option(int which, int value);
 

@@ -125,6 +125,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true", help="one dtype, fewer shapes")
     ap.add_argument("--out", default=None)
+    ap.add_argument("--only", default=None, choices=["gemm", "fmha", "decode"], help="one path only")
     args = ap.parse_args(argv)
     dev = torch.device("cuda", torch.cuda.current_device())
     sink = open(args.out, "w") if args.out else None
@@ -136,18 +137,22 @@ def main(argv=None):
             sink.write(line + "\n")
             sink.flush()
 
-    emit(gemm_case(1024, 1024, 1024, torch.float16, dev, n=50))
-    dtypes = [torch.bfloat16] if args.quick else [torch.bfloat16, torch.float16]
-    for dtype in dtypes:
-        for (K, N) in inputs.LLAMA7B_KN:
-            for M in inputs.LLM_M + [64]:
-                emit(gemm_case(M, K, N, dtype, dev))
-    emit(fmha_case(1, 32, 8, 4096, 128, True, torch.float16, dev, n=30))
-    for D in (64, 128):
-        for S in ((2048,) if args.quick else (1024, 2048, 8192)):
-            for causal in (False, True):
-                emit(fmha_case(8, 32, 32, S, D, causal, torch.bfloat16, dev))
-    emit(decode_case(dev))
+    want = lambda path: args.only in (None, path)
+    if want("gemm"):
+        emit(gemm_case(1024, 1024, 1024, torch.float16, dev, n=50))
+        dtypes = [torch.bfloat16] if args.quick else [torch.bfloat16, torch.float16]
+        for dtype in dtypes:
+            for (K, N) in inputs.LLAMA7B_KN:
+                for M in inputs.LLM_M + [64]:
+                    emit(gemm_case(M, K, N, dtype, dev))
+    if want("fmha"):
+        emit(fmha_case(1, 32, 8, 4096, 128, True, torch.float16, dev, n=30))
+        for D in (64, 128):
+            for S in ((2048,) if args.quick else (1024, 2048, 8192)):
+                for causal in (False, True):
+                    emit(fmha_case(8, 32, 32, S, D, causal, torch.bfloat16, dev))
+    if want("decode"):
+        emit(decode_case(dev))
     if sink:
         sink.close()
     return 0

@@ -198,6 +198,32 @@ def test_kernel_variants_agree(cuda_device, variant):
     _assert_close(o, ref, absref=absref)
 
 
+@pytest.mark.parametrize("variant", [0, 2, 12])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_d64_separate_and_shared_p_buffers(cuda_device, variant, dtype):
+    """Head dimension 64 can keep P in TMEM columns of its own (B200K_OPT_FMHA_SPLIT_P = 1), so that the next
+    block's QK^T is issued ahead of this block's PV product; by default P goes over its S columns.  Both orders
+    of issue meet the oracle on the shapes that stress the hand-overs (many blocks per tile, tiles with
+    different block counts under the causal mask, ragged ends, GQA, keys beyond 4096 for the
+    one-item-per-CTA kernel) and agree with each other within the tolerance."""
+    from b200k import _lib, fmha, inputs
+    cases = [(2, 8, 2, 700, 700, True), (1, 4, 4, 300, 5000, False), (1, 2, 1, 1500, 1500, True),
+             (3, 4, 4, 130, 130, False)]
+    for (B, Hq, Hkv, Sq, Skv, causal) in cases:
+        q, k, v = inputs.fmha_inputs(B, Hq, Hkv, Sq, Skv, 64, dtype, seed=Sq + Skv)
+        qd, kd, vd = q.to(cuda_device), k.to(cuda_device), v.to(cuda_device)
+        ref, absref = _refs(q, k, v, causal)
+        outs = []
+        for mode in (1, 0):
+            with _lib.option(_lib.OPT_FMHA_SPLIT_P, mode):
+                o = fmha.fmha_fwd(qd, kd, vd, causal=causal, variant=variant)
+                o2 = fmha.fmha_fwd(qd, kd, vd, causal=causal, variant=variant)
+            assert torch.equal(o, o2)
+            _assert_close(o, ref, where=(Sq, Skv, causal, mode), absref=absref)
+            outs.append(o)
+        assert float((outs[0].float() - outs[1].float()).abs().max()) <= 2 * TOL + float(ref.abs().max()) * 2.0 ** -7
+
+
 @pytest.mark.parametrize("variant", [2, 12])
 @pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])

@@ -54,6 +54,9 @@ static_assert(256 * kSoftmaxRegs + 128 * kAuxRegs <= kFmhaThreads * launch_regs(
 #ifndef B200K_FMHA_P_PARTS
 #define B200K_FMHA_P_PARTS 2
 #endif
+#ifndef B200K_FMHA_MAX_CHAINS
+#define B200K_FMHA_MAX_CHAINS 4  // independent dependency chains of the row maximum (4 or 8)
+#endif
 // P is handed to the MMA warp in kPParts pieces (1, 2 or 4) of 128 / kPParts keys, so that the PV
 // product of the first pieces runs while the softmax group still exponentiates the later ones.
 constexpr int kPParts = B200K_FMHA_P_PARTS;
@@ -67,16 +70,30 @@ static_assert(kPParts == 1 || kPParts == 2 || kPParts == 4, "P is handed over in
 // Used by the one-item-per-CTA kernel (measured +4 % at d = 64, +10 % together with 3 of 8 exponentials
 // emulated); the persistent kernel, whose items are short, measured 1-6 % slower with it (the PV
 // product is a quarter longer) and keeps the sums in registers.
+// Decoupled score and probability buffers (head dimension 64 only).  With P written over the S columns
+// it came from, the next block's QK^T of a tile can only be issued after this block's PV product has
+// consumed P, so a tile's chain per block is softmax -> PV -> QK^T -> softmax and its softmax group
+// idles while the tensor pipe works for it (at d = 64 it waited for S a quarter to a third of the time).
+// At d = 64 the two O accumulators take 2 x 64 columns, which leaves room for P buffers of their own
+// (S0, S1, O0, O1, P0, P1 = 128 + 128 + 64 + 64 + 64 + 64 = 512): the MMA warp then issues S(j+1) of a
+// tile as soon as its softmax group has pulled S(j) into registers, and the group goes from block to
+// block without waiting for the tensor pipe.  Two more barriers per tile carry the new hazards:
+// `s_free` (S columns may be overwritten) and `p_free` (PV(j) has read P(j): P(j+1) may be stored, and O
+// may be rescaled - with S(j+1) issued ahead of PV(j), a finished S no longer implies a finished PV).
+template <int D>
+constexpr bool kCanSplitP = D == 64;
 template <int D, bool PERSISTENT>
-constexpr bool kSumOnTensor = D == 64 && !PERSISTENT;
-template <int D, bool PERSISTENT>
-constexpr uint32_t kOCols = D + (kSumOnTensor<D, PERSISTENT> ? 16 : 0);  // accumulator columns of one tile
+constexpr bool kHasOnesBox = D == 64 && !PERSISTENT;  // shared-memory layout: a ones box behind every V stage
+template <int D, bool PERSISTENT, bool SPLITP>
+constexpr bool kSumOnTensor = kHasOnesBox<D, PERSISTENT> && !SPLITP;  // its 16 extra O columns do not fit beside P0, P1
+template <int D, bool PERSISTENT, bool SPLITP>
+constexpr uint32_t kOCols = D + (kSumOnTensor<D, PERSISTENT, SPLITP> ? 16 : 0);  // accumulator columns of one tile
 
 template <int D>
 struct FmhaSmem {
   static constexpr uint32_t kTileBytes = kTile * D * 2;  // one Q tile, K block or V block
   static constexpr uint32_t kHalfBytes = kTile * 128;    // one 64-wide (128-byte) column box
-  static constexpr uint32_t kVStride = kTileBytes + (kSumOnTensor<D, false> ? kHalfBytes : 0);  // V stage (+ ones box)
+  static constexpr uint32_t kVStride = kTileBytes + (kHasOnesBox<D, false> ? kHalfBytes : 0);  // V stage (+ ones box)
   static constexpr uint32_t kQOff = 0;
   static constexpr uint32_t kKOff = 2 * kTileBytes;
   static constexpr uint32_t kVOff = 4 * kTileBytes;
@@ -87,7 +104,7 @@ struct FmhaSmem {
 // fills the ones boxes behind both V stages (all threads of the CTA, before the roles split)
 template <int D, bool BF16, bool PERSISTENT, typename L>
 __device__ __forceinline__ void fill_ones_boxes(uint8_t* smem) {
-  if constexpr (kSumOnTensor<D, PERSISTENT>) {
+  if constexpr (kHasOnesBox<D, PERSISTENT>) {
     const uint32_t one2 = BF16 ? 0x3f803f80u : 0x3c003c00u;
     const uint4 w = make_uint4(one2, one2, one2, one2);
     for (int s = 0; s < 2; ++s) {
@@ -196,22 +213,54 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
 // row of the warp, so P may reach 2^threshold.
 //   lim: local index of the last visible key of this row in this block (masked = some row of the tile
 //   has lim < 127); s_tmem / o_tmem: this thread's lane of the S and O accumulators.
-template <int D, bool BF16, int EMU, bool SUMTC>
-__device__ __forceinline__ void softmax_block(uint32_t s_tmem, uint32_t o_tmem, bool first, bool masked, int lim,
-                                              float sc, float& m_use, float& l, uint64_t* p_part_i,
-                                              uint64_t* p_ready_i) {
+//   SPLITP (decoupled buffers): P goes to p_tmem instead of over S; once the row is in registers the
+//   group releases the S columns (`s_free_i`, when another block follows), and it waits for the previous
+//   block's PV product (`p_free_i`, parity `p_free_phase`, when `wait_p_free`) before it rescales O or
+//   stores the first P.  Returns false if that wait ran out.
+template <int D, bool BF16, int EMU, bool SUMTC, bool SPLITP>
+__device__ __forceinline__ bool softmax_block(uint32_t s_tmem, uint32_t p_tmem, uint32_t o_tmem, bool first,
+                                              bool masked, int lim, float sc, float& m_use, float& l,
+                                              uint64_t* p_part_i, uint64_t* p_ready_i, uint64_t* s_free_i,
+                                              bool signal_s_free, uint64_t* p_free_i, bool wait_p_free,
+                                              uint32_t p_free_phase) {
   uint32_t s[128];
   tmem_ld32(s_tmem + 0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
   tmem_ld32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
   tmem_ld32(s_tmem + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
   tmem_ld32(s_tmem + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
   tmem_ld_wait();
+  bool ok = true;
+  if constexpr (SPLITP) {
+    if (signal_s_free) {  // the row is in registers: the next block's scores may overwrite these columns
+      tc_fence_before();
+      mbar_arrive(s_free_i);
+    }
+  }
+  bool pv_done = !SPLITP || !wait_p_free;
+  auto wait_prev_pv = [&]() {
+    if (!pv_done) {
+      if (!mbar_wait(p_free_i, p_free_phase)) ok = false;
+      tc_fence_after();
+      pv_done = true;
+    }
+  };
   if (masked) {
 #pragma unroll
     for (int k = 0; k < 128; ++k)
       if (k > lim) s[k] = 0xff800000u;  // -inf
   }
   auto row_max = [&]() {
+#if B200K_FMHA_MAX_CHAINS == 8
+    float mx[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) mx[c] = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < 128; k += 16) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) mx[c] = max3(mx[c], __uint_as_float(s[k + 2 * c]), __uint_as_float(s[k + 2 * c + 1]));
+    }
+    return fmaxf(max3(mx[0], mx[1], mx[2]), fmaxf(max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]))) * sc;
+#else
     float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
     for (int k = 0; k < 128; k += 8) {
@@ -221,6 +270,7 @@ __device__ __forceinline__ void softmax_block(uint32_t s_tmem, uint32_t o_tmem, 
       mx3 = max3(mx3, __uint_as_float(s[k + 6]), __uint_as_float(s[k + 7]));
     }
     return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc;
+#endif
   };
   // moves m to m_new: l and the O accumulator (the PV products of the earlier blocks are complete:
   // this block's S was issued behind them) are scaled by 2^(m - m_new)
@@ -288,15 +338,18 @@ __device__ __forceinline__ void softmax_block(uint32_t s_tmem, uint32_t o_tmem, 
     const float m_new = fmaxf(m_use, row_max());
     if (first)
       m_use = m_new;
-    else if (__any_sync(0xffffffffu, (m_new - m_use) > kRescaleThreshold))
+    else if (__any_sync(0xffffffffu, (m_new - m_use) > kRescaleThreshold)) {
+      wait_prev_pv();  // O must hold every earlier product before it is scaled
       rescale_to(m_new);
+    }
   }
   uint64_t sum_a = f2pack(0.f, 0.f), sum_b = f2pack(0.f, 0.f);
 #pragma unroll
   for (int qt = 0; qt < 4; ++qt) {
     uint32_t pk[16];
     quarter(qt, pk, sum_a, sum_b);
-    tmem_st16(s_tmem + qt * 16, pk);
+    if (qt == 0) wait_prev_pv();  // the previous block's P has been consumed
+    tmem_st16(p_tmem + qt * 16, pk);
     // hand the finished piece to the MMA warp (the last piece goes through p_ready below)
     if (qt < 3 && (qt + 1) % (4 / kPParts) == 0) {
       tmem_st_wait();
@@ -312,19 +365,26 @@ __device__ __forceinline__ void softmax_block(uint32_t s_tmem, uint32_t o_tmem, 
     f2unpack(add2(sum_a, sum_b), a, b);
     l += a + b;
   }
+  return ok;
 }
 
 
 // EMU: how many of every 8 score pairs take their exponentials on the FMA pipe (0..4).
-template <int D, bool BF16, int EMU>
+template <int D, bool BF16, int EMU, bool SPLITP>
 __global__ void __launch_bounds__(kFmhaThreads, 1)
 fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                 const FmhaParams p) {
+  static_assert(!SPLITP || kCanSplitP<D>, "separate P buffers need the spare TMEM columns of d = 64");
   using L = FmhaSmem<D>;
   constexpr int kDBoxes = D / 64;  // 64-wide column boxes per row
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kSCol0 = 0, kSCol1 = 128, kOCol0 = 256, kOCol1 = 256 + kOCols<D, false>;
+  constexpr bool kSumTc = kSumOnTensor<D, false, SPLITP>;
+  constexpr uint32_t kOW = kOCols<D, false, SPLITP>;
+  constexpr uint32_t kSCol0 = 0, kSCol1 = 128, kOCol0 = 256, kOCol1 = 256 + kOW;
+  // P over its own S columns, or (SPLITP) in 64 columns of its own behind the accumulators
+  constexpr uint32_t kPCol0 = SPLITP ? 256 + 2 * kOW : kSCol0, kPCol1 = SPLITP ? 256 + 2 * kOW + 64 : kSCol1;
+  static_assert(!SPLITP || kPCol1 + 64 <= kTmemCols, "TMEM map exceeds 512 columns");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -338,7 +398,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* p_ready = bars + 12;  // [2]
   uint64_t* o_full = bars + 14;   // [2]
   uint64_t* p_part = bars + 16;   // [3][2]  piece 0, 1, 2 of P stored (the last piece signals p_ready)
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 22);
+  uint64_t* s_free = bars + 22;   // [2]  (SPLITP) S_i is in the softmax group's registers
+  uint64_t* p_free = bars + 24;   // [2]  (SPLITP) PV_i of a block has read P_i (and updated O_i)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 26);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -389,6 +451,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&p_ready[i], 128);
       for (int part = 0; part < 3; ++part) mbar_init(&p_part[part * 2 + i], 128);
       mbar_init(&o_full[i], 1);
+      mbar_init(&s_free[i], 128);
+      mbar_init(&p_free[i], 1);
     }
     fence_mbar_init();
     prefetch_tmap(&tmQ);
@@ -446,12 +510,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     reg_dealloc<kAuxRegs>();
     if (elect_one() && nb_max > 0) {
       constexpr uint32_t idesc_s = make_idesc_f16(BF16 ? 1 : 0, 0, 0, kTile, kTile);
-      constexpr uint32_t idesc_pv = make_idesc_f16(BF16 ? 1 : 0, 0, 1, kTile, kOCols<D, false>);
+      constexpr uint32_t idesc_pv = make_idesc_f16(BF16 ? 1 : 0, 0, 1, kTile, kOW);
       const uint32_t q_addr = smem_u32(smem + L::kQOff);
       const uint32_t k_addr = smem_u32(smem + L::kKOff);
       const uint32_t v_addr = smem_u32(smem + L::kVOff);
       const uint32_t s_col[2] = {kSCol0, kSCol1};
       const uint32_t o_col[2] = {kOCol0, kOCol1};
+      const uint32_t p_col[2] = {kPCol0, kPCol1};
       bool ok = true;
       auto fail = [&]() {
         report_timeout(p.status, KID_FMHA, ROLE_MMA);
@@ -476,10 +541,27 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t va = v_addr + stage * L::kVStride;
 #pragma unroll
         for (int kk = kk0; kk < kk1; ++kk) {
-          umma_ts(tmem_base + o_col[i], tmem_base + s_col[i] + kk * 8,
+          umma_ts(tmem_base + o_col[i], tmem_base + p_col[i] + kk * 8,
                   make_smem_desc_sw128(va + kk * 2048, L::kHalfBytes, 1024), idesc_pv,
                   (!first || kk > 0) ? 1u : 0u);
         }
+      };
+      // PV_i of block j as the pieces of P arrive; false if a wait ran out
+      auto pv_block = [&](int i, int stage, int j) {
+        constexpr int kStepsPerPart = kTile / 16 / kPParts;
+#pragma unroll
+        for (int part = 0; part + 1 < kPParts; ++part) {
+          if (ok && !mbar_wait(&p_part[part * 2 + i], j & 1)) fail();
+          if (!ok) return;
+          tc_fence_after();
+          issue_pv(i, stage, j == 0, part * kStepsPerPart, (part + 1) * kStepsPerPart);
+        }
+        if (!mbar_wait(&p_ready[i], j & 1)) {
+          fail();
+          return;
+        }
+        tc_fence_after();
+        issue_pv(i, stage, j == 0, (kPParts - 1) * kStepsPerPart, kTile / 16);
       };
       if (!mbar_wait(&k_full[0], 0)) fail();
       for (int i = 0; i < 2 && ok; ++i) {
@@ -496,45 +578,70 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int j = 0; j < nb_max && ok; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&v_full[s], ph)) {
-          fail();
-          break;
-        }
-        bool k_next_ready = false;
-        for (int i = 0; i < 2 && ok; ++i) {
-          if (j >= nb[i]) continue;
-          constexpr int kStepsPerPart = kTile / 16 / kPParts;
-#pragma unroll
-          for (int part = 0; part + 1 < kPParts; ++part) {
-            if (ok && !mbar_wait(&p_part[part * 2 + i], j & 1)) fail();
-            if (!ok) break;
-            tc_fence_after();
-            issue_pv(i, s, j == 0, part * kStepsPerPart, (part + 1) * kStepsPerPart);
-          }
-          if (!ok) break;
-          if (!mbar_wait(&p_ready[i], j & 1)) {
-            fail();
-            break;
-          }
-          tc_fence_after();
-          issue_pv(i, s, j == 0, (kPParts - 1) * kStepsPerPart, kTile / 16);
-          if (j == nb[i] - 1) umma_commit<1>(&o_full[i]);
-          if (j + 1 < nb[i]) {
+        if constexpr (SPLITP) {
+          // The next block's scores first: they need K(j+1) and the S columns, which a softmax group
+          // releases as soon as it holds S(j) in registers - not this block's PV products.
+          if (j + 1 < nb_max) {
             const int s1 = (j + 1) & 1;
-            if (!k_next_ready) {
-              if (!mbar_wait(&k_full[s1], ((j + 1) >> 1) & 1)) {
+            if (!mbar_wait(&k_full[s1], ((j + 1) >> 1) & 1)) {
+              fail();
+              break;
+            }
+            for (int i = 0; i < 2 && ok; ++i) {
+              if (j + 1 >= nb[i]) continue;
+              if (!mbar_wait(&s_free[i], j & 1)) {
                 fail();
                 break;
               }
               tc_fence_after();
-              k_next_ready = true;
+              issue_s(i, s1);
             }
-            issue_s(i, s1);
+            if (!ok) break;
+            umma_commit<1>(&k_empty[s1]);
           }
+          if (!mbar_wait(&v_full[s], ph)) {
+            fail();
+            break;
+          }
+          for (int i = 0; i < 2 && ok; ++i) {
+            if (j >= nb[i]) continue;
+            pv_block(i, s, j);
+            if (!ok) break;
+            if (j == nb[i] - 1)
+              umma_commit<1>(&o_full[i]);
+            else
+              umma_commit<1>(&p_free[i]);  // the group may store P(j+1) and rescale O
+          }
+          if (!ok) break;
+          umma_commit<1>(&v_empty[s]);
+        } else {
+          if (!mbar_wait(&v_full[s], ph)) {
+            fail();
+            break;
+          }
+          bool k_next_ready = false;
+          for (int i = 0; i < 2 && ok; ++i) {
+            if (j >= nb[i]) continue;
+            pv_block(i, s, j);
+            if (!ok) break;
+            if (j == nb[i] - 1) umma_commit<1>(&o_full[i]);
+            if (j + 1 < nb[i]) {
+              const int s1 = (j + 1) & 1;
+              if (!k_next_ready) {
+                if (!mbar_wait(&k_full[s1], ((j + 1) >> 1) & 1)) {
+                  fail();
+                  break;
+                }
+                tc_fence_after();
+                k_next_ready = true;
+              }
+              issue_s(i, s1);
+            }
+          }
+          if (!ok) break;
+          umma_commit<1>(&v_empty[s]);
+          if (j + 1 < nb_max) umma_commit<1>(&k_empty[(j + 1) & 1]);
         }
-        if (!ok) break;
-        umma_commit<1>(&v_empty[s]);
-        if (j + 1 < nb_max) umma_commit<1>(&k_empty[(j + 1) & 1]);
       }
     }
   } else {
@@ -545,6 +652,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t s_tmem = tmem_base + lane_sel + (i == 0 ? kSCol0 : kSCol1);
     const uint32_t o_tmem = tmem_base + lane_sel + (i == 0 ? kOCol0 : kOCol1);
+    const uint32_t p_tmem = tmem_base + lane_sel + (i == 0 ? kPCol0 : kPCol1);
     if (valid[i]) {
       const float sc = p.scale_log2;
       const int q = q0[i] + row;
@@ -563,8 +671,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tc_fence_after();
         const int k0 = j * kTile;
-        softmax_block<D, BF16, EMU, kSumOnTensor<D, false>>(s_tmem, o_tmem, j == 0, k0 + kTile - 1 > tile_min_lim, lim_row - k0, sc, m_use, l,
-                                    &p_part[i], &p_ready[i]);
+        if (!softmax_block<D, BF16, EMU, kSumTc, SPLITP>(
+                s_tmem, p_tmem, o_tmem, j == 0, k0 + kTile - 1 > tile_min_lim, lim_row - k0, sc, m_use, l, &p_part[i],
+                &p_ready[i], &s_free[i], j + 1 < nb[i], &p_free[i], j > 0, (uint32_t)((j - 1) & 1))) {
+          if (lane == 0) report_timeout(p.status, KID_FMHA, ROLE_SOFTMAX);
+          ok = false;
+          break;
+        }
       }
 
       // ------------------------------ epilogue ------------------------------
@@ -576,7 +689,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_after();
       }
       if (ok) {
-        if constexpr (kSumOnTensor<D, false>) {
+        if constexpr (kSumTc) {
           if (nb[i] > 0) {  // the denominator was summed by the PV products: 16 equal columns behind O
             const uint32_t t = tmem_ld1(o_tmem + D);
             tmem_ld_wait();
@@ -647,7 +760,7 @@ struct FmhaPSmem {
   static constexpr uint32_t kHalfBytes = kTile * 128;
   static constexpr uint32_t kQOff = 0;
   static constexpr uint32_t kKOff = 2 * kTileBytes;
-  static constexpr uint32_t kVStride = kTileBytes + (kSumOnTensor<D, true> ? kHalfBytes : 0);  // V stage (+ ones box)
+  static constexpr uint32_t kVStride = kTileBytes + (kHasOnesBox<D, true> ? kHalfBytes : 0);  // V stage (+ ones box)
   static constexpr uint32_t kVOff = 4 * kTileBytes;
   static constexpr uint32_t kStageOff = kVOff + 2 * kVStride;  // 2 x 16 KB output staging
   static constexpr uint32_t kBarOff = kStageOff + 2 * kHalfBytes;
@@ -692,15 +805,20 @@ __device__ __forceinline__ FmhaItem fmha_item(const FmhaParams& p, int idx) {
   return it;
 }
 
-template <int D, bool BF16, int EMU>
+template <int D, bool BF16, int EMU, bool SPLITP>
 __global__ void __launch_bounds__(kFmhaThreads, 1)
 fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                            const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                            const FmhaParams p, int total_items) {
+  static_assert(!SPLITP || kCanSplitP<D>, "separate P buffers need the spare TMEM columns of d = 64");
   using L = FmhaPSmem<D>;
   constexpr int kDBoxes = D / 64;
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kSCol0 = 0, kSCol1 = 128, kOCol0 = 256, kOCol1 = 256 + kOCols<D, true>;
+  constexpr bool kSumTc = kSumOnTensor<D, true, SPLITP>;
+  constexpr uint32_t kOW = kOCols<D, true, SPLITP>;
+  constexpr uint32_t kSCol0 = 0, kSCol1 = 128, kOCol0 = 256, kOCol1 = 256 + kOW;
+  constexpr uint32_t kPCol0 = SPLITP ? 256 + 2 * kOW : kSCol0, kPCol1 = SPLITP ? 256 + 2 * kOW + 64 : kSCol1;
+  static_assert(!SPLITP || kPCol1 + 64 <= kTmemCols, "TMEM map exceeds 512 columns");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -716,7 +834,9 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
   uint64_t* o_full = bars + 16;    // [2]  last PV of the item done
   uint64_t* o_free = bars + 18;    // [2]  epilogue has read O_i out of TMEM
   uint64_t* p_part = bars + 20;    // [3][2]  piece 0, 1, 2 of P stored (the last piece signals p_ready)
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 26);
+  uint64_t* s_free = bars + 26;    // [2]  (SPLITP) S_i is in the softmax group's registers
+  uint64_t* p_free = bars + 28;    // [2]  (SPLITP) PV_i of a block has read P_i (and updated O_i)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 30);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -740,6 +860,8 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       for (int part = 0; part < 3; ++part) mbar_init(&p_part[part * 2 + i], 128);
       mbar_init(&o_full[i], 1);
       mbar_init(&o_free[i], 128);
+      mbar_init(&s_free[i], 128);
+      mbar_init(&p_free[i], 1);
     }
     fence_mbar_init();
     prefetch_tmap(&tmQ);
@@ -814,13 +936,14 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     reg_dealloc<kPersistAuxRegs>();
     if (elect_one()) {
       constexpr uint32_t idesc_s = make_idesc_f16(BF16 ? 1 : 0, 0, 0, kTile, kTile);
-      constexpr uint32_t idesc_pv = make_idesc_f16(BF16 ? 1 : 0, 0, 1, kTile, kOCols<D, true>);
+      constexpr uint32_t idesc_pv = make_idesc_f16(BF16 ? 1 : 0, 0, 1, kTile, kOW);
       const uint32_t q_addr = smem_u32(smem + L::kQOff);
       const uint32_t k_addr = smem_u32(smem + L::kKOff);
       const uint32_t v_addr = smem_u32(smem + L::kVOff);
       const uint32_t s_col[2] = {kSCol0, kSCol1};
       const uint32_t o_col[2] = {kOCol0, kOCol1};
-      uint32_t kc = 0, vc = 0, qn[2] = {0, 0}, pn[2] = {0, 0}, on[2] = {0, 0};
+      const uint32_t p_col[2] = {kPCol0, kPCol1};
+      uint32_t kc = 0, vc = 0, qn[2] = {0, 0}, pn[2] = {0, 0}, on[2] = {0, 0}, sfn[2] = {0, 0};
       bool ok = true;
       auto fail = [&]() {
         report_timeout(p.status, KID_FMHA, ROLE_MMA);
@@ -841,10 +964,33 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         const uint32_t va = v_addr + stage * L::kVStride;
 #pragma unroll
         for (int kk = kk0; kk < kk1; ++kk) {
-          umma_ts(tmem_base + o_col[i], tmem_base + s_col[i] + kk * 8,
+          umma_ts(tmem_base + o_col[i], tmem_base + p_col[i] + kk * 8,
                   make_smem_desc_sw128(va + kk * 2048, L::kHalfBytes, 1024), idesc_pv,
                   (!first || kk > 0) ? 1u : 0u);
         }
+      };
+      // PV_i of block j of the item as the pieces of P arrive (the item's first one also waits until the
+      // previous item's O_i has been read out); ok turns false if a wait ran out
+      auto pv_block = [&](int i, int j) {
+        if (j == 0 && !mbar_wait(&o_free[i], (on[i] & 1) ^ 1)) {
+          fail();
+          return;
+        }
+        constexpr int kStepsPerPart = kTile / 16 / kPParts;
+#pragma unroll
+        for (int part = 0; part + 1 < kPParts; ++part) {
+          if (ok && !mbar_wait(&p_part[part * 2 + i], pn[i] & 1)) fail();
+          if (!ok) return;
+          tc_fence_after();
+          issue_pv(i, vc & 1, j == 0, part * kStepsPerPart, (part + 1) * kStepsPerPart);
+        }
+        if (!mbar_wait(&p_ready[i], pn[i] & 1)) {
+          fail();
+          return;
+        }
+        ++pn[i];
+        tc_fence_after();
+        issue_pv(i, vc & 1, j == 0, (kPParts - 1) * kStepsPerPart, kTile / 16);
       };
       for (int r = 0; r * (int)gridDim.x < total_items && ok; ++r) {
         const int w = snake_item(r);
@@ -869,57 +1015,88 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         umma_commit<1>(&k_empty[kc & 1]);
         ++kc;
         for (int j = 0; j < it.nb_max && ok; ++j) {
-          if (!mbar_wait(&v_full[vc & 1], (vc >> 1) & 1)) {
-            fail();
-            break;
-          }
-          bool k_next_ready = false;
-          for (int i = 0; i < 2 && ok; ++i) {
-            if (j >= it.nb[i]) continue;
-            if (j == 0 && !mbar_wait(&o_free[i], (on[i] & 1) ^ 1)) {  // previous item's O_i was read out
-              fail();
-              break;
-            }
-            constexpr int kStepsPerPart = kTile / 16 / kPParts;
-#pragma unroll
-            for (int part = 0; part + 1 < kPParts; ++part) {
-              if (ok && !mbar_wait(&p_part[part * 2 + i], pn[i] & 1)) fail();
-              if (!ok) break;
-              tc_fence_after();
-              issue_pv(i, vc & 1, j == 0, part * kStepsPerPart, (part + 1) * kStepsPerPart);
-            }
-            if (!ok) break;
-            if (!mbar_wait(&p_ready[i], pn[i] & 1)) {
-              fail();
-              break;
-            }
-            ++pn[i];
-            tc_fence_after();
-            issue_pv(i, vc & 1, j == 0, (kPParts - 1) * kStepsPerPart, kTile / 16);
-            if (j == it.nb[i] - 1) {
-              umma_commit<1>(&o_full[i]);
-              ++on[i];
-              umma_commit<1>(&q_free[i]);  // covers the item's last S_i as well
-              ++qn[i];
-            }
-            if (j + 1 < it.nb[i]) {
-              if (!k_next_ready) {
-                if (!mbar_wait(&k_full[kc & 1], (kc >> 1) & 1)) {
+          if constexpr (SPLITP) {
+            // the next block's scores first (they do not depend on this block's PV products)
+            if (j + 1 < it.nb_max) {
+              if (!mbar_wait(&k_full[kc & 1], (kc >> 1) & 1)) {
+                fail();
+                break;
+              }
+              for (int i = 0; i < 2 && ok; ++i) {
+                if (j + 1 >= it.nb[i]) continue;
+                if (!mbar_wait(&s_free[i], sfn[i] & 1)) {
                   fail();
                   break;
                 }
+                ++sfn[i];
                 tc_fence_after();
-                k_next_ready = true;
+                issue_s(i, kc & 1);
+                if (j + 2 == it.nb[i]) {
+                  umma_commit<1>(&q_free[i]);  // that was the item's last read of Q_i
+                  ++qn[i];
+                }
               }
-              issue_s(i, kc & 1);
+              if (!ok) break;
+              umma_commit<1>(&k_empty[kc & 1]);
+              ++kc;
             }
-          }
-          if (!ok) break;
-          umma_commit<1>(&v_empty[vc & 1]);
-          ++vc;
-          if (j + 1 < it.nb_max) {
-            umma_commit<1>(&k_empty[kc & 1]);
-            ++kc;
+            if (!mbar_wait(&v_full[vc & 1], (vc >> 1) & 1)) {
+              fail();
+              break;
+            }
+            for (int i = 0; i < 2 && ok; ++i) {
+              if (j >= it.nb[i]) continue;
+              pv_block(i, j);
+              if (!ok) break;
+              if (j == it.nb[i] - 1) {
+                umma_commit<1>(&o_full[i]);
+                ++on[i];
+                if (it.nb[i] == 1) {  // single-block item: the prologue's S_i was the only read of Q_i
+                  umma_commit<1>(&q_free[i]);
+                  ++qn[i];
+                }
+              } else {
+                umma_commit<1>(&p_free[i]);
+              }
+            }
+            if (!ok) break;
+            umma_commit<1>(&v_empty[vc & 1]);
+            ++vc;
+          } else {
+            if (!mbar_wait(&v_full[vc & 1], (vc >> 1) & 1)) {
+              fail();
+              break;
+            }
+            bool k_next_ready = false;
+            for (int i = 0; i < 2 && ok; ++i) {
+              if (j >= it.nb[i]) continue;
+              pv_block(i, j);
+              if (!ok) break;
+              if (j == it.nb[i] - 1) {
+                umma_commit<1>(&o_full[i]);
+                ++on[i];
+                umma_commit<1>(&q_free[i]);  // covers the item's last S_i as well
+                ++qn[i];
+              }
+              if (j + 1 < it.nb[i]) {
+                if (!k_next_ready) {
+                  if (!mbar_wait(&k_full[kc & 1], (kc >> 1) & 1)) {
+                    fail();
+                    break;
+                  }
+                  tc_fence_after();
+                  k_next_ready = true;
+                }
+                issue_s(i, kc & 1);
+              }
+            }
+            if (!ok) break;
+            umma_commit<1>(&v_empty[vc & 1]);
+            ++vc;
+            if (j + 1 < it.nb_max) {
+              umma_commit<1>(&k_empty[kc & 1]);
+              ++kc;
+            }
           }
         }
       }
@@ -932,10 +1109,11 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t s_tmem = tmem_base + lane_sel + (i == 0 ? kSCol0 : kSCol1);
     const uint32_t o_tmem = tmem_base + lane_sel + (i == 0 ? kOCol0 : kOCol1);
+    const uint32_t p_tmem = tmem_base + lane_sel + (i == 0 ? kPCol0 : kPCol1);
     uint8_t* stage = smem + L::kStageOff + i * L::kHalfBytes;
     const float sc = p.scale_log2;
     const int off = p.kv_len - p.Sq;
-    uint32_t sn = 0, itn = 0;
+    uint32_t sn = 0, itn = 0, pfn = 0;
     bool ok = true;
     bool store_pending = false;
     for (int r = 0; r * (int)gridDim.x < total_items && ok; ++r) {
@@ -957,8 +1135,14 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         ++sn;
         tc_fence_after();
         const int k0 = j * kTile;
-        softmax_block<D, BF16, EMU, kSumOnTensor<D, true>>(s_tmem, o_tmem, j == 0, k0 + kTile - 1 > tile_min_lim, lim_row - k0, sc, m_use, l,
-                                    &p_part[i], &p_ready[i]);
+        if (!softmax_block<D, BF16, EMU, kSumTc, SPLITP>(
+                s_tmem, p_tmem, o_tmem, j == 0, k0 + kTile - 1 > tile_min_lim, lim_row - k0, sc, m_use, l, &p_part[i],
+                &p_ready[i], &s_free[i], j + 1 < it.nb[i], &p_free[i], j > 0, pfn & 1)) {
+          if (lane == 0) report_timeout(p.status, KID_FMHA, ROLE_SOFTMAX);
+          ok = false;
+          break;
+        }
+        if (SPLITP && j > 0) ++pfn;
       }
       if (!ok) break;
 
@@ -972,7 +1156,7 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         }
         ++itn;
         tc_fence_after();
-        if constexpr (kSumOnTensor<D, true>) {  // the denominator was summed by the PV products
+        if constexpr (kSumTc) {  // the denominator was summed by the PV products
           const uint32_t t = tmem_ld1(o_tmem + D);
           tmem_ld_wait();
           l = __uint_as_float(t);
@@ -1038,14 +1222,14 @@ int make_map_bhsd(CUtensorMap* tm, const void* base, int D, int S, int H, int B,
   return encode_tmap_16bit(tm, base, 4, dims, strides, box, 1);
 }
 
-template <int D, bool BF16, int EMU>
+template <int D, bool BF16, int EMU, bool SPLITP>
 int launch_fmha(const void* Q, const void* K, const void* V, void* O, int B, int Hq, int Hkv, int Sq, int kv_len,
                 const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, float scale, int causal,
                 bool persistent, cudaStream_t stream) {
   using L = FmhaSmem<D>;
   using LP = FmhaPSmem<D>;
-  auto kfn = fmha_fwd_kernel<D, BF16, EMU>;
-  auto kfn_p = fmha_fwd_persistent_kernel<D, BF16, EMU>;
+  auto kfn = fmha_fwd_kernel<D, BF16, EMU, SPLITP>;
+  auto kfn_p = fmha_fwd_persistent_kernel<D, BF16, EMU, SPLITP>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1128,16 +1312,25 @@ extern "C" int b200k_fmha_fwd(const void* Q, const void* K, const void* V, void*
   static const int kEmuOfCode[5] = {0, 2, 4, 1, 3};
   const int code = (variant % 10) - 1;
   if (variant != 0 && (code < 0 || code > 4 || variant >= 20)) return B200K_EARG;
-  // measured best: 2 of 8 emulated, except the one-item kernel at d = 64 (row sums on the tensor pipe), 3 of 8
-  const int emu = variant != 0 ? kEmuOfCode[code] : (D == 64 && !persistent) ? 3 : kDefaultEmu;
-#define B200K_FMHA(DD, BF, EM)                                                                                  \
-  launch_fmha<DD, BF, EM>(Q, K, V, O, B, Hq, Hkv, Sq, kv_len, q_strides, k_strides, v_strides, o_strides, scale, \
-                          causal, persistent, stream)
-#define B200K_FMHA_EMU(DD, BF)                                                                  \
-  (emu == 0 ? B200K_FMHA(DD, BF, 0) : emu == 1 ? B200K_FMHA(DD, BF, 1) : emu == 2 ? B200K_FMHA(DD, BF, 2) \
-   : emu == 3 ? B200K_FMHA(DD, BF, 3) : B200K_FMHA(DD, BF, 4))
-  if (D == 128) return bf16 ? B200K_FMHA_EMU(128, true) : B200K_FMHA_EMU(128, false);
-  return bf16 ? B200K_FMHA_EMU(64, true) : B200K_FMHA_EMU(64, false);
+  // d = 64: P in TMEM columns of its own (the next block's QK^T no longer waits for this block's PV)
+  // when B200K_OPT_FMHA_SPLIT_P = 1 asks for it.  Measured on B200 against P over its S columns
+  // (bf16, B = 8, 32 heads): -5 % / +1 % at s = 1024 (full / causal), -3 % / +2 % at 2048, -5 % / -10 % at
+  // 8192, where it also displaces the row sums on the tensor pipe: the softmax groups no longer wait for
+  // S, and the block period does not move, because the two softmax warps that share a scheduler then
+  // contend for its issue slots and MUFU instead of taking turns.  Kept selectable, off by default.
+  const bool split_p = D == 64 && tuning_option(B200K_OPT_FMHA_SPLIT_P) == 1;
+  // measured best: 2 of 8 emulated, except the one-item kernel at d = 64 with its row sums on the tensor
+  // pipe (shared S/P columns only), 3 of 8
+  const int emu = variant != 0 ? kEmuOfCode[code] : (D == 64 && !persistent && !split_p) ? 3 : kDefaultEmu;
+#define B200K_FMHA(DD, BF, EM, SP)                                                                                  \
+  launch_fmha<DD, BF, EM, SP>(Q, K, V, O, B, Hq, Hkv, Sq, kv_len, q_strides, k_strides, v_strides, o_strides, scale, \
+                              causal, persistent, stream)
+#define B200K_FMHA_EMU(DD, BF, SP)                                                                              \
+  (emu == 0 ? B200K_FMHA(DD, BF, 0, SP) : emu == 1 ? B200K_FMHA(DD, BF, 1, SP) : emu == 2 ? B200K_FMHA(DD, BF, 2, SP) \
+   : emu == 3 ? B200K_FMHA(DD, BF, 3, SP) : B200K_FMHA(DD, BF, 4, SP))
+  if (D == 128) return bf16 ? B200K_FMHA_EMU(128, true, false) : B200K_FMHA_EMU(128, false, false);
+  if (split_p) return bf16 ? B200K_FMHA_EMU(64, true, true) : B200K_FMHA_EMU(64, false, true);
+  return bf16 ? B200K_FMHA_EMU(64, true, false) : B200K_FMHA_EMU(64, false, false);
 #undef B200K_FMHA_EMU
 #undef B200K_FMHA
 }
