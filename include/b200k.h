@@ -259,6 +259,15 @@ int b200k_device_supported(void);
  *   B200K_OPT_DECODE_HEADS_PER_CTA  h >= 1: decode grid of (split, groups of h KV heads, sequence)
  *   B200K_OPT_FMHA_PERSISTENT       1 = persistent prefill kernel, 2 = one work item per CTA
  *                                   (the environment variable says 1 / 0)
+ *   B200K_OPT_SKINNY_PAIR           weight-streaming GEMM, M <= 64: 1 = clusters of three CTAs over two 128-column
+ *                                   slabs each wherever that can run (measured slower; never chosen otherwise)
+ *   B200K_OPT_PDL                   programmatic dependent launch of the GEMM and prefill kernels.  Default: a
+ *                                   kernel may start (barriers, TMEM, tensor-map prefetch) while the kernel before
+ *                                   it in the stream is still running and waits for that kernel before it reads
+ *                                   an operand or writes an output.  1 = in addition the caller states that the
+ *                                   weight of a weight-streaming GEMM (M <= 128) is a constant, not written by the
+ *                                   preceding kernel: its first tiles are requested before that wait.  2 = plain
+ *                                   launches.
  *   B200K_OPT_FMHA_SPLIT_P          head_dim 64: 1 = P goes to TMEM columns of its own, so that the next
  *                                   block's QK^T is issued ahead of this block's PV product (measured
  *                                   no faster than P over its S columns, the default)
@@ -271,7 +280,9 @@ enum {
   B200K_OPT_DECODE_HEADS_PER_CTA = 2,
   B200K_OPT_FMHA_PERSISTENT = 3,
   B200K_OPT_FMHA_SPLIT_P = 4,
-  B200K_OPT_COUNT = 5
+  B200K_OPT_SKINNY_PAIR = 5,
+  B200K_OPT_PDL = 6,
+  B200K_OPT_COUNT = 7
 };
 int b200k_set_option(int which, int value);
 

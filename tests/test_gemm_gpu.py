@@ -237,6 +237,94 @@ def test_skinny_column_window_ragged_n(cuda_device, skinny_splits, M, N, splits)
     assert bool((big[:, N:] == 7.0).all())
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 256, 512), (16, 264, 520), (33, 1160, 1024), (64, 1288, 4096), (64, 11008, 4096),
+                                   (7, 12288, 576), (48, 384, 8192)])
+def test_skinny_two_slabs_per_cluster(cuda_device, shape, dtype):
+    """The paired-slab decomposition of the weight-streaming GEMM (clusters of three CTAs over two 128-column
+    slabs, the middle CTA holding two accumulators), forced on wherever it can run: even and odd slab
+    counts (an odd last slab is paired with columns beyond N), ragged N and K, all three epilogues,
+    bit-identical reruns, and the same result as the one-slab-per-cluster decomposition within rounding."""
+    from b200k import _lib, gemm
+    M, N, K = shape
+    a, b = _inputs(M, N, K, dtype, seed=M + N + K, std_b=0.05)
+    ad, bd = a.to(cuda_device), b.to(cuda_device)
+    ref = oracle.gemm_ref(a, b)
+    n0 = _lib.launch_count()
+    with _lib.option(_lib.OPT_SKINNY_PAIR, 1):
+        c1 = gemm.gemm(ad, bd, variant=3)
+        c2 = gemm.gemm(ad, bd, variant=3)
+        g = torch.Generator().manual_seed(5)
+        r = torch.randn(M, N, generator=g).to(dtype)
+        cadd = gemm.gemm_add(ad, bd, r.to(cuda_device))
+        cswi = gemm.gemm_swiglu(ad, bd) if N % 16 == 0 else None
+    with _lib.option(_lib.OPT_SKINNY_PAIR, 2):
+        c0 = gemm.gemm(ad, bd, variant=3)
+    assert torch.equal(c1, c2)
+    assert oracle.rel_frobenius(c1, ref) <= TOL
+    assert oracle.rel_frobenius(c1, c0.float().cpu()) <= 2e-3     # same products, other summation split
+    assert oracle.rel_frobenius(cadd, ref + r.float()) <= TOL
+    if cswi is not None:
+        assert oracle.rel_frobenius(cswi, torch.nn.functional.silu(ref[:, 0::2]) * ref[:, 1::2]) <= TOL
+    # a column window of a wider output: nothing outside it is written
+    big = torch.full((M, N + 24), 7.0, dtype=dtype, device=cuda_device)
+    with _lib.option(_lib.OPT_SKINNY_PAIR, 1):
+        gemm.gemm(ad, bd, out=big[:, 8:8 + N], variant=3)
+    assert torch.equal(big[:, 8:8 + N], c1) and bool((big[:, :8] == 7.0).all()) and bool((big[:, 8 + N:] == 7.0).all())
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_skinny_dependent_launch_chain(cuda_device, mode):
+    """Programmatic dependent launch of the weight-streaming GEMM: a launch may begin while the kernel
+    before it in the stream still runs and must wait for it before it reads its activations or writes C.
+    A chain in which every GEMM consumes the previous one's output (as the projections of a decode step
+    do), launched back to back without host synchronisation and also replayed from a CUDA graph, gives
+    the bits of the same chain with plain launches (mode 2); mode 1 additionally requests the first weight
+    tiles before the wait (weights here are constants).  In the default mode the weight itself may have
+    been written by the kernel just before (filled on the device, then multiplied at once)."""
+    from b200k import _lib, gemm
+    M, K = 48, 1024
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(cuda_device)
+    ws = [(torch.randn(K, K, generator=g) * 0.03).to(torch.bfloat16).to(cuda_device) for _ in range(6)]
+
+    def chain():
+        y = x
+        for w in ws:
+            y = gemm.gemm(y, w, variant=3)
+        return y
+
+    with _lib.option(_lib.OPT_PDL, 2):
+        want = chain()
+    torch.cuda.synchronize()
+    with _lib.option(_lib.OPT_PDL, mode):
+        got = [chain() for _ in range(5)]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            chain()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = chain()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        assert all(torch.equal(y, want) for y in got) and torch.equal(out, want)
+        if mode != 1:
+            # the weight is produced by the kernel right before the GEMM, again and again
+            w = torch.empty(K, 1536, dtype=torch.bfloat16, device=cuda_device)
+            for i in range(8):
+                w.fill_(0.001 * (i + 1))
+                y = gemm.gemm(x, w, variant=3)
+                ref = x.float().sum(dim=1, keepdim=True) * (torch.tensor(0.001 * (i + 1)).bfloat16().float())
+                assert torch.allclose(y.float(), ref.expand(-1, 1536), rtol=2e-2, atol=2e-2), i
+    ref = x.float().cpu()
+    for w in ws:
+        ref = (ref @ w.float().cpu()).to(torch.bfloat16).float()
+    assert oracle.rel_frobenius(want, ref) <= 2e-2
+
+
 def test_skinny_rejects_large_m(cuda_device):
     from b200k import _lib, gemm
     a = torch.zeros(256, 64, dtype=torch.float16, device=cuda_device)

@@ -80,8 +80,9 @@ def test_gemm_oracle_vs_reference_rungs_vs_library(reference_outputs, cuda_devic
         got = torch.from_numpy(ref[f"gemm_{rung}"]).float()
         # the reference's own acceptance window, with the oracle in the place of `a @ b`
         assert torch.allclose(got, want, rtol=1e-1, atol=1e-1), rung
-        # what the rungs actually achieve with fp16 accumulation over K = 256
-        assert oracle.rel_frobenius(got, want) <= 2e-2, (rung, oracle.rel_frobenius(got, want))
+        # what the rungs actually achieve with fp16 accumulation over K = 256 (observed on B200: 6.0e-4,
+        # max-abs 0.087; the library on the same tensors: 2.1e-4)
+        assert oracle.rel_frobenius(got, want) <= 2e-3, (rung, oracle.rel_frobenius(got, want))
     for idx in (0, 8, 11, 12):
         c = gemm_unified.ops.fine_gemm(a.to(cuda_device), b.to(cuda_device), idx)
         assert oracle.rel_frobenius(c, want) <= oracle.GEMM_REL_FRO_TOL
@@ -104,6 +105,9 @@ def test_fmha_oracle_vs_reference_rungs_vs_library(reference_outputs, cuda_devic
         assert not torch.isnan(got).any()
         # kernels/fmha/test/correct.py:55: allclose(rtol=0, atol=5e-2)
         assert torch.allclose(got, want, rtol=0, atol=5e-2), (rung, oracle.max_abs(got, want))
+        # what the rungs actually achieve on these inputs (observed on B200: 1.7e-4 .. 2.9e-4 with their
+        # fp16 softmax state; the library: 1.1e-5 .. 7.2e-5)
+        assert oracle.max_abs(got, want) <= 1e-3, (rung, oracle.max_abs(got, want))
     # the library on the same tensors, inside its own bar, through the reference-facing wrapper
     for idx in (2, 4, 5):
         o = fmha_unified.ops.fine_fmha(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), causal, False, idx)

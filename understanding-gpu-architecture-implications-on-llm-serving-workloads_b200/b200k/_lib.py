@@ -90,7 +90,7 @@ def check(code: int, where: str) -> None:
         raise B200KError(code, where)
 
 
-OPT_SKINNY_S, OPT_SKINNY_BN, OPT_DECODE_HEADS_PER_CTA, OPT_FMHA_PERSISTENT, OPT_FMHA_SPLIT_P = 0, 1, 2, 3, 4
+OPT_SKINNY_S, OPT_SKINNY_BN, OPT_DECODE_HEADS_PER_CTA, OPT_FMHA_PERSISTENT, OPT_FMHA_SPLIT_P, OPT_SKINNY_PAIR, OPT_PDL = 0, 1, 2, 3, 4, 5, 6
 
 
 class option:

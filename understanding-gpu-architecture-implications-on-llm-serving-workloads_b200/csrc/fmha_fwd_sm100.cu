@@ -468,6 +468,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // programmatic dependent launch: everything above (barriers, TMEM, tensor-map prefetch) may have run while
+  // the kernel before this one in the stream was still running; nothing of Q, K, V is read and nothing of O
+  // written before that kernel has finished
+  grid_launch_dependents();
+  grid_dependency_wait();
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp >= 10) {
@@ -877,6 +882,8 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  grid_launch_dependents();  // programmatic dependent launch, as in the one-item kernel
+  grid_dependency_wait();
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp >= 10) {
@@ -1263,14 +1270,32 @@ int launch_fmha(const void* Q, const void* K, const void* V, void* O, int B, int
   if (!p.status) return B200K_ECUDA;
   const long grid = (long)p.num_pairs * Hq * B;
   if (grid <= 0 || grid > 0x7fffffffL) return B200K_ESHAPE;
+  // launched so that the set-up may overlap the tail of the kernel before it in the stream (the kernels
+  // wait for that kernel before they touch Q, K, V or O); B200K_OPT_PDL = 2 asks for a plain launch
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kFmhaThreads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = tuning_option(B200K_OPT_PDL) == 2 ? 0 : 1;
+  cudaError_t e;
   if (persistent) {
     const int sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
-    const unsigned ctas = (unsigned)(grid < sms ? grid : sms);
-    kfn_p<<<ctas, kFmhaThreads, LP::kTotal, stream>>>(tmQ, tmK, tmV, tmO, p, (int)grid);
+    cfg.gridDim = dim3((unsigned)(grid < sms ? grid : sms));
+    cfg.dynamicSmemBytes = LP::kTotal;
+    e = cudaLaunchKernelEx(&cfg, kfn_p, tmQ, tmK, tmV, tmO, p, (int)grid);
   } else {
-    kfn<<<(unsigned)grid, kFmhaThreads, L::kTotal, stream>>>(tmQ, tmK, tmV, tmO, p);
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.dynamicSmemBytes = L::kTotal;
+    e = cudaLaunchKernelEx(&cfg, kfn, tmQ, tmK, tmV, tmO, p);
   }
   count_launch();
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return B200K_ECUDA;
+  }
   return check_launch();
 }
 

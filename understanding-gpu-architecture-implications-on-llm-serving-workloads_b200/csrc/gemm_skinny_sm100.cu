@@ -53,8 +53,16 @@ constexpr int kSkDrainGroups = 2;  // groups of four draining warps
 // BN = weight columns per CTA (256 or 128): BN/128 MMAs of 128 weight columns per k-step, a weight
 // tile of BN*64*2 bytes per stage (32 or 16 KB), a partial tile of MPAD*BN floats.
 
-template <int MPAD, int BN>
+// T = slabs per cluster.  T = 1: one slab per cluster of S CTAs (above).  T = 2 (128-column slabs, push
+// scheme only): a cluster of 3 CTAs streams TWO neighbouring slabs, its k-blocks laid end to end and cut
+// into three equal ranges (CTA 0: the first two thirds of slab 0; CTA 1: the rest of slab 0 and the first
+// third of slab 1, in two accumulators; CTA 2: the rest of slab 1).  For weights whose slabs alone leave a
+// third of the SMs idle (N = 11008: 86 slabs) this puts 129 CTAs to work on two thirds of a slab each
+// instead of 86 on a whole one.  The 256 columns of the pair are split into three owner slices; a column
+// has at most two contributors, which push into slot (rank - first contributor of the column's slab).
+template <int MPAD, int BN, int T = 1>
 struct SkinnySmem {
+  static_assert(T == 1 || (T == 2 && BN == 128 && MPAD <= 64), "two slabs per cluster: narrow slabs, push scheme");
   static constexpr int kSkBN = BN;
   static constexpr uint32_t kSkWBytes = BN * kSkBK * 2;
   static constexpr uint32_t kXBytes = MPAD * kSkBK * 2;  // activation tile of one stage
@@ -65,7 +73,8 @@ struct SkinnySmem {
   // scheme (a tile that reuses the drained stage buffers): narrow slab up to 64 rows +8..10 %, wide slab
   // at 16 rows +3..5 %; wide slab at 32 rows -5 % (the fifth stage goes), 128 rows -5..-17 % (two of six).
   static constexpr bool kPush = (BN == 128 && MPAD <= 64) || (BN == 256 && MPAD <= 16);
-  static constexpr uint32_t kRecvBytes = kPush ? MPAD * (BN + 32) * 4 : 0;
+  // T = 2: two slots of MPAD rows of ceil(64 chunks / 3 CTAs) * 4 = 88 columns
+  static constexpr uint32_t kRecvBytes = !kPush ? 0 : T == 2 ? MPAD * (2 * 88) * 4 : MPAD * (BN + 32) * 4;
   // one CTA per SM: as many stages as fit in ~208 KB next to the receive buffer, at most 6 (8 narrow)
   static constexpr int kMaxStages = BN == 256 ? 6 : 8;
   static constexpr int kFit = (208 * 1024 - kRecvBytes) / kStageBytes;
@@ -134,17 +143,18 @@ __device__ __forceinline__ uint32_t pack2s(float lo, float hi) {
   }
 }
 
-template <int MPAD, bool BF16, int EPI, int BN>
+template <int MPAD, bool BF16, int EPI, int BN, int T = 1>
 __global__ void __launch_bounds__(kSkThreads, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                    uint16_t* __restrict__ C, int64_t ldc, int M, int N, int K, int* status,
-                   const uint16_t* __restrict__ R, int64_t ldr) {
-  using L = SkinnySmem<MPAD, BN>;
+                   const uint16_t* __restrict__ R, int64_t ldr, int early_weights) {
+  using L = SkinnySmem<MPAD, BN, T>;
   constexpr int kStages = L::kStages;
   constexpr int kSkBN = BN, kSkSub = BN / 128;
+  constexpr int kSpan = T * BN;                         // columns a cluster produces
   constexpr uint32_t kSkWBytes = L::kSkWBytes;
   constexpr uint32_t kAccCols = MPAD < 32 ? 32 : MPAD;  // TMEM columns of one accumulator
-  constexpr uint32_t kTmemCols = kSkSub * kAccCols;
+  constexpr uint32_t kTmemCols = T * kSkSub * kAccCols;  // T = 2: one accumulator per slab this CTA touches
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
@@ -156,19 +166,33 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
   const int lane = threadIdx.x & 31;
   const uint32_t S = cluster_size_x();
   const uint32_t rank = cluster_ctarank();
-  const int n0 = (blockIdx.x / S) * kSkBN;
+  const int n0 = (blockIdx.x / S) * kSpan;  // first column of the cluster's slab (of its pair of slabs)
   const int num_kb = (K + kSkBK - 1) / kSkBK;
-  const int kb_begin = (int)((int64_t)rank * num_kb / S);
-  const int kb_end = (int)((int64_t)(rank + 1) * num_kb / S);
+  // This CTA's range of the cluster's k-blocks; with T = 2 the index runs over slab 0's k-blocks and then
+  // slab 1's (index / num_kb = slab, index % num_kb = k-block).
+  const int kb_begin = (int)((int64_t)rank * (T * num_kb) / S);
+  const int kb_end = (int)((int64_t)(rank + 1) * (T * num_kb) / S);
+  const int slab_first = T == 1 ? 0 : kb_begin / num_kb;  // slab of this CTA's first accumulator
 
-  auto load_stage = [&](int kb, uint32_t stage) {
+  // a stage = the weight tile (kSkBN columns x 64 k-rows) and the activation tile (MPAD rows x 64 k); the
+  // two halves can be issued apart (the barrier counts the bytes of both)
+  auto load_stage_w = [&](int kb, uint32_t stage) {
     uint8_t* sw = smem + stage * L::kStageBytes;
-    uint8_t* sx = sw + kSkWBytes;
+    const int slab = T == 1 ? 0 : kb / num_kb;
+    const int k0 = (kb - slab * num_kb) * kSkBK;
     mbar_expect_tx(&full_bar[stage], kSkWBytes + L::kXBytes);
 #pragma unroll
     for (int j = 0; j < kSkBN / 64; ++j)
-      tma_load_2d(sw + j * (kSkBK * 128), &tmW, &full_bar[stage], n0 + j * 64, kb * kSkBK);
-    tma_load_2d(sx, &tmX, &full_bar[stage], kb * kSkBK, 0);
+      tma_load_2d(sw + j * (kSkBK * 128), &tmW, &full_bar[stage], n0 + slab * kSkBN + j * 64, k0);
+  };
+  auto load_stage_x = [&](int kb, uint32_t stage) {
+    uint8_t* sx = smem + stage * L::kStageBytes + kSkWBytes;
+    const int slab = T == 1 ? 0 : kb / num_kb;
+    tma_load_2d(sx, &tmX, &full_bar[stage], (kb - slab * num_kb) * kSkBK, 0);
+  };
+  auto load_stage = [&](int kb, uint32_t stage) {
+    load_stage_w(kb, stage);
+    load_stage_x(kb, stage);
   };
   // k-blocks whose loads thread 0 issues right after initialising the barriers, while the TMEM
   // allocation and the CTA-wide sync are still under way (every stage is free at that point)
@@ -184,7 +208,20 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     }
     mbar_init(tmem_full, 1);
     fence_mbar_init();
-    for (int kb = kb_begin; kb < kb_pre; ++kb) load_stage(kb, (uint32_t)(kb - kb_begin));
+    // Programmatic dependent launch: this kernel may have started while the one before it in the stream
+    // is still running, so that its set-up (and the launch gap) hide under that kernel's tail; it waits
+    // for that kernel here, before the first byte is requested.  With `early_weights` (the caller states
+    // that the weight is a constant of the model, not something the preceding kernel wrote) the WEIGHTS of
+    // the first ring are requested before the wait, which also hides the first HBM round trip; the
+    // activations may be the previous kernel's output and always come after it.
+    if (early_weights)
+      for (int kb = kb_begin; kb < kb_pre; ++kb) load_stage_w(kb, (uint32_t)(kb - kb_begin));
+    grid_launch_dependents();  // the next kernel of the stream may start its own set-up
+    grid_dependency_wait();
+    for (int kb = kb_begin; kb < kb_pre; ++kb) {
+      if (!early_weights) load_stage_w(kb, (uint32_t)(kb - kb_begin));
+      load_stage_x(kb, (uint32_t)(kb - kb_begin));
+    }
   }
   if (warp == 1) {
     tmem_alloc<1>(tmem_holder, kTmemCols);
@@ -193,6 +230,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  grid_dependency_wait();  // every thread that reads R or writes C is ordered behind the previous kernel
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp == 0) {
@@ -227,14 +265,18 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         tc_fence_after();
         const uint32_t w_addr = smem_u32(smem + stage * L::kStageBytes);
         const uint64_t xdesc = make_smem_desc_sw128(w_addr + kSkWBytes, 16, 1024);
+        // T = 2: the accumulator of the slab this k-block belongs to; it starts afresh at the CTA's first
+        // k-block and at the first k-block of a slab
+        const int seg = T == 1 ? 0 : kb / num_kb - slab_first;
+        const bool fresh = kb == kb_begin || (T == 2 && kb % num_kb == 0);
 #pragma unroll
         for (int sub = 0; sub < kSkSub; ++sub) {
           // weight columns [128*sub, 128*sub+128): two 64-column boxes
           const uint64_t wdesc = make_smem_desc_sw128(w_addr + sub * 2 * (kSkBK * 128), kSkBK * 128, 1024);
 #pragma unroll
           for (int k = 0; k < kSkBK / 16; ++k)
-            umma_ss<1>(tmem_base + sub * kAccCols, wdesc + (uint64_t)(k * 128), xdesc + (uint64_t)(k * 2), idesc,
-                       (kb > kb_begin || k > 0) ? 1u : 0u);
+            umma_ss<1>(tmem_base + (seg * kSkSub + sub) * kAccCols, wdesc + (uint64_t)(k * 128),
+                       xdesc + (uint64_t)(k * 2), idesc, (!fresh || k > 0) ? 1u : 0u);
         }
         umma_commit<1>(&empty_bar[stage]);
         if (++stage == kStages) {
@@ -270,9 +312,13 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     float* tile = reinterpret_cast<float*>(smem);
     constexpr int kChunk = MPAD < 32 ? 16 : 32;
     int piece = 0;
+    // T = 2: one pass per accumulator (per slab this CTA streamed a part of); a CTA whose range ends
+    // inside its first slab has only the first
+    const int num_acc = T == 1 ? kSkSub : (have ? (kb_end - 1) / num_kb - slab_first + 1 : 0);
 #pragma unroll 1
-    for (int sub = 0; sub < kSkSub; ++sub) {
-      const int n = sub * 128 + ew * 32 + lane;
+    for (int sub = 0; sub < num_acc; ++sub) {
+      // column inside the cluster's span of kSpan columns
+      const int n = (T == 1 ? sub * 128 : (slab_first + sub) * kSkBN) + ew * 32 + lane;
 #pragma unroll 1
       for (int cb = 0; cb < MPAD / kChunk; ++cb, ++piece) {
         if (cb * kChunk >= M) break;
@@ -292,15 +338,25 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         if (L::kPush && S > 1) {
           // Push this CTA's partial of column n into slot `rank` of the receive buffer of the CTA that
           // owns the column's 16-byte chunk: consecutive lanes, consecutive words (plain remote stores).
-          const int c = n >> 2;                                          // chunk of 4 columns of the slab
-          const int owner = ((c + 1) * (int)S - 1) / (kSkBN / 4);        // r with c_begin(r) <= c < c_end(r)
-          const int c_first = owner * (kSkBN / 4) / (int)S;              // first chunk of the owner's slice
-          const int wmax = 4 * ((kSkBN / 4 + (int)S - 1) / (int)S);      // floats per row of a slot
+          const int c = n >> 2;                                          // chunk of 4 columns of the span
+          const int owner = ((c + 1) * (int)S - 1) / (kSpan / 4);        // r with c_begin(r) <= c < c_end(r)
+          const int c_first = owner * (kSpan / 4) / (int)S;              // first chunk of the owner's slice
+          const int wmax = 4 * ((kSpan / 4 + (int)S - 1) / (int)S);      // floats per row of a slot
+          // slot: the source's rank (T = 1: every CTA contributes to every column), or its position among
+          // the contributors of the column's slab (T = 2: the first one is the first rank whose range ends
+          // beyond the slab's first k-block)
+          int slot = (int)rank;
+          if constexpr (T == 2) {
+            const int slab_kb0 = (slab_first + sub) * num_kb;
+            int first = 0;
+            while ((int)((int64_t)(first + 1) * (T * num_kb) / S) <= slab_kb0) ++first;
+            slot = (int)rank - first;
+          }
           uint32_t base;
           asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
                        : "=r"(base)
                        : "r"(smem_u32(smem + L::kRecvOff)), "r"((uint32_t)owner));
-          base += (uint32_t)(((int)rank * MPAD * wmax + (n - 4 * c_first)) * 4);
+          base += (uint32_t)((slot * MPAD * wmax + (n - 4 * c_first)) * 4);
 #pragma unroll
           for (int e = 0; e < kChunk; ++e) {
             const int m = cb * kChunk + e;
@@ -361,9 +417,21 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 
   if (S > 1) {
     // this CTA's slice of the tile's 16-byte chunks (any S in 1..8 divides them unevenly at most by one)
-    const int c_begin = (int)rank * (kSkBN / 4) / (int)S;
-    const int c_end = ((int)rank + 1) * (kSkBN / 4) / (int)S;
+    const int c_begin = (int)rank * (kSpan / 4) / (int)S;
+    const int c_end = ((int)rank + 1) * (kSpan / 4) / (int)S;
     const int w4 = c_end - c_begin;
+    // T = 2: how many CTAs contributed to each slab (those whose k-block range meets the slab's)
+    int contributors[T];
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+      contributors[t] = 0;
+      if constexpr (T == 2) {
+        for (int r = 0; r < (int)S; ++r) {
+          const int b = (int)((int64_t)r * (T * num_kb) / S), e = (int)((int64_t)(r + 1) * (T * num_kb) / S);
+          if (e > b && e > t * num_kb && b < (t + 1) * num_kb) ++contributors[t];
+        }
+      }
+    }
     const uint32_t tile_addr = smem_u32(smem);
     // base address of every peer's tile in rank order (this CTA's own included)
     uint32_t peer[8];
@@ -379,33 +447,35 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       const int step_r = kSkThreads / w4, step_c = kSkThreads % w4;
       for (; row < M; row += step_r) {
         const int n = n0 + (c_begin + c) * 4;
-        const uint32_t off = (uint32_t)(row * kSkBN + (c_begin + c) * 4) * 4u;
+        const uint32_t off = (uint32_t)(row * kSkBN + (c_begin + c) * 4) * 4u;  // pull scheme (T = 1) only
         // partial of source CTA s: pushed into this CTA's receive buffer (narrow slab), or read from the
         // source's own tile through distributed shared memory (wide slab)
         auto part = [&](uint32_t s) -> float4 {
           if constexpr (L::kPush) {
-            const int wmax = 4 * ((kSkBN / 4 + (int)S - 1) / (int)S);
+            const int wmax = 4 * ((kSpan / 4 + (int)S - 1) / (int)S);
             return *reinterpret_cast<const float4*>(smem + L::kRecvOff +
                                                     (((int)s * MPAD + row) * wmax + c * 4) * 4);
           } else {
             return ld_dsmem_f4(peer[s] + off);
           }
         };
-        float4 acc = part(0), v1, v2, v3;
-        if (S > 1) v1 = part(1);
-        if (S > 2) v2 = part(2);
-        if (S > 3) v3 = part(3);
+        // sources of this chunk: all S CTAs, or (T = 2) the contributors of the chunk's slab, slots 0..
+        const uint32_t nsrc = T == 1 ? S : (uint32_t)contributors[(c_begin + c) / (kSkBN / 4) < T ? (c_begin + c) / (kSkBN / 4) : T - 1];
+        float4 acc = nsrc > 0 ? part(0) : make_float4(0.f, 0.f, 0.f, 0.f), v1, v2, v3;
+        if (nsrc > 1) v1 = part(1);
+        if (nsrc > 2) v2 = part(2);
+        if (nsrc > 3) v3 = part(3);
         auto add = [&](const float4& v) {
           acc.x += v.x;
           acc.y += v.y;
           acc.z += v.z;
           acc.w += v.w;
         };
-        if (S > 1) add(v1);
-        if (S > 2) add(v2);
-        if (S > 3) add(v3);
+        if (nsrc > 1) add(v1);
+        if (nsrc > 2) add(v2);
+        if (nsrc > 3) add(v3);
 #pragma unroll 1
-        for (uint32_t s = 4; s < S; ++s) add(part(s));
+        for (uint32_t s = 4; s < nsrc; ++s) add(part(s));
         if (n < N) {
           if constexpr (EPI == 2) {
             // columns n..n+3 are (gate, up), (gate, up) of outputs n/2 and n/2+1
@@ -487,12 +557,12 @@ int skinny_cluster_size(int N, int K, int bn) {
   return s;
 }
 
-template <int MPAD, bool BF16, int EPI, int BN>
+template <int MPAD, bool BF16, int EPI, int BN, int T = 1>
 static int launch_skinny_t(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
                            int64_t ldc, cudaStream_t stream, const void* R, int64_t ldr) {
-  using L = SkinnySmem<MPAD, BN>;
+  using L = SkinnySmem<MPAD, BN, T>;
   constexpr int kSkBN = BN;
-  auto kfn = gemm_skinny_kernel<MPAD, BF16, EPI, BN>;
+  auto kfn = gemm_skinny_kernel<MPAD, BF16, EPI, BN, T>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -520,22 +590,29 @@ static int launch_skinny_t(const void* A, const void* B, void* C, int M, int N, 
   }
   int* status = status_ptr();
   if (!status) return B200K_ECUDA;
-  const int S = skinny_cluster_size(N, K, kSkBN);
-  const int tiles = (N + kSkBN - 1) / kSkBN;
+  // T = 2: clusters of three CTAs, each over a pair of slabs (an odd last slab is paired with columns
+  // beyond N, which load as zeros and store nothing)
+  const int S = T == 2 ? 3 : skinny_cluster_size(N, K, kSkBN);
+  const int tiles = ((N + kSkBN - 1) / kSkBN + T - 1) / T;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(tiles * S));
   cfg.blockDim = dim3(kSkThreads);
   cfg.dynamicSmemBytes = L::kTotal;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = (unsigned)S;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // programmatic dependent launch (see the kernel's prologue); B200K_OPT_PDL: 2 = off, 1 = weights are
+  // constants and may be requested before the previous kernel has finished
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  const int pdl = tuning_option(B200K_OPT_PDL);
+  cfg.numAttrs = pdl == 2 ? 1 : 2;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kfn, tmX, tmW, reinterpret_cast<uint16_t*>(C), ldc, M, N, K, status,
-                                     reinterpret_cast<const uint16_t*>(R), ldr);
+                                     reinterpret_cast<const uint16_t*>(R), ldr, pdl == 1 ? 1 : 0);
   count_launch();
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
@@ -549,17 +626,34 @@ int launch_skinny(const void* A, const void* B, void* C, int M, int N, int K, in
   if (M > 128 || epilogue < 0 || epilogue > 2) return B200K_ESHAPE;
   // tiny M on a wide weight: the epilogue is negligible and 512-byte rows stream a little better
   const bool narrow = skinny_slab_width(N) == 128 && !(M <= 32 && (N + 127) / 128 > 64 && !tuning_option(B200K_OPT_SKINNY_BN));
-#define B200K_SKINNY_B(MP, EP, BNN)                                                                      \
-  (bf16 ? launch_skinny_t<MP, true, EP, BNN>(A, B, C, M, N, K, lda, ldb, ldc, stream, R, ldr)            \
-        : launch_skinny_t<MP, false, EP, BNN>(A, B, C, M, N, K, lda, ldb, ldc, stream, R, ldr))
-#define B200K_SKINNY_E(MP, EP) (narrow ? B200K_SKINNY_B(MP, EP, 128) : B200K_SKINNY_B(MP, EP, 256))
+  // Two slabs per cluster of three CTAs (SkinnySmem's T = 2), meant for weights of 75..98 narrow slabs,
+  // where one CTA per slab leaves a third or more of the SMs without weight bytes to stream and two CTAs
+  // per slab would not fit one wave.  Measured on B200 (graph-replayed, bf16, K = 4096) it LOSES: N = 11008
+  // (129 instead of 86 CTAs) 5.34 -> 4.56 TB/s at M = 1, 4.72 -> 4.04 at M = 64; N = 12288 (144 CTAs) halves,
+  // because 48 clusters of three do not all fit the GPCs at once.  86 CTAs already stream at 6.2 TB/s, so
+  // what the extra CTAs add to the loop is less than the push, cluster barrier and reduction cost that
+  // a cluster of one does not pay.  Kept behind B200K_OPT_SKINNY_PAIR = 1 (tests cover it); never chosen.
+  const int slabs128 = (N + 127) / 128, num_kb = (K + kSkBK - 1) / kSkBK;
+  const int sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
+  const bool pair_can = M <= 64 && num_kb >= 8 && (slabs128 + 1) / 2 * 3 <= sms && slabs128 >= 2 &&
+                        tuning_option(B200K_OPT_SKINNY_S) == 0 && tuning_option(B200K_OPT_SKINNY_BN) != 256;
+  const int pair_opt = tuning_option(B200K_OPT_SKINNY_PAIR);
+  const bool pair = pair_opt == 1 && pair_can;
+#define B200K_SKINNY_B(MP, EP, BNN, TT)                                                                      \
+  (bf16 ? launch_skinny_t<MP, true, EP, BNN, TT>(A, B, C, M, N, K, lda, ldb, ldc, stream, R, ldr)            \
+        : launch_skinny_t<MP, false, EP, BNN, TT>(A, B, C, M, N, K, lda, ldb, ldc, stream, R, ldr))
+#define B200K_SKINNY_E(MP, EP) (narrow ? B200K_SKINNY_B(MP, EP, 128, 1) : B200K_SKINNY_B(MP, EP, 256, 1))
+#define B200K_SKINNY_P(MP, EP) (pair ? B200K_SKINNY_B(MP, EP, 128, 2) : B200K_SKINNY_E(MP, EP))
 #define B200K_SKINNY(MP) \
-  return epilogue == 0 ? B200K_SKINNY_E(MP, 0) : epilogue == 1 ? B200K_SKINNY_E(MP, 1) : B200K_SKINNY_E(MP, 2)
+  return epilogue == 0 ? B200K_SKINNY_P(MP, 0) : epilogue == 1 ? B200K_SKINNY_P(MP, 1) : B200K_SKINNY_P(MP, 2)
   if (M <= 16) { B200K_SKINNY(16); }
   if (M <= 32) { B200K_SKINNY(32); }
   if (M <= 64) { B200K_SKINNY(64); }
+#undef B200K_SKINNY_P
+#define B200K_SKINNY_P(MP, EP) B200K_SKINNY_E(MP, EP)
   B200K_SKINNY(128);
 #undef B200K_SKINNY
+#undef B200K_SKINNY_P
 #undef B200K_SKINNY_E
 #undef B200K_SKINNY_B
 }

@@ -152,6 +152,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   if constexpr (CTAS == 2) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
+  // programmatic dependent launch: the set-up above may have overlapped the tail of the kernel before this
+  // one in the stream; no operand is read and no output written before that kernel has finished
+  grid_launch_dependents();
+  grid_dependency_wait();
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp == 0) {
@@ -504,13 +508,15 @@ int launch_tc(const void* A, const void* B, void* const* Cs, int num_dst, int M,
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = L::kTotal;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CTAS;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // B200K_OPT_PDL = 2: plain launch
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = tuning_option(B200K_OPT_PDL) == 2 ? 1 : 2;
   // n-blocks per rasterisation group (see tile_coords): 16 when a group is then still about one wave of
   // tiles or less per m-row count (at least 16 rows of tiles) and its B columns take at most 40 MB of L2
   const int num_m = (M + kBM * CTAS - 1) / (kBM * CTAS);

@@ -141,7 +141,8 @@ std::atomic<int> g_options[B200K_OPT_COUNT];
 std::once_flag g_options_once;
 void read_options_from_env() {
   static const char* const names[B200K_OPT_COUNT] = {"B200K_SKINNY_S", "B200K_SKINNY_BN", "B200K_DECODE_HEADS_PER_CTA",
-                                                     "B200K_FMHA_PERSISTENT", "B200K_FMHA_SPLIT_P"};
+                                                     "B200K_FMHA_PERSISTENT", "B200K_FMHA_SPLIT_P",
+                                                     "B200K_SKINNY_PAIR", "B200K_PDL"};
   for (int i = 0; i < B200K_OPT_COUNT; ++i) {
     const char* e = getenv(names[i]);
     int v = e ? atoi(e) : 0;

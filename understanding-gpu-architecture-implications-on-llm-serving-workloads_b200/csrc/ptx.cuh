@@ -30,6 +30,15 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute
+// may start while the kernel before it in the stream is still running; `grid_dependency_wait` blocks until
+// that kernel has completed and its memory operations are visible (it returns at once when the launch
+// carried no such attribute), so everything before it must touch only memory the previous kernel does
+// not write.  `grid_launch_dependents` lets the next such kernel start once every CTA of this grid has
+// issued it or exited.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(
