@@ -399,7 +399,8 @@ def test_error_codes(cuda_device):
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(128, 256, 64), (300, 520, 200), (1024, 4096, 512), (4096, 4096, 1024),
-                                   (1, 256, 192), (8, 4096, 1024), (33, 1024, 2112), (64, 2048, 4096), (100, 520, 200)])
+                                   (1, 256, 192), (8, 4096, 1024), (33, 1024, 2112), (64, 2048, 4096), (100, 520, 200),
+                                   (100, 11008, 520)])
 def test_fused_residual_add(cuda_device, shape, dtype):
     """C = A.B + R with the add in the epilogue (fp32 before the single rounding): M <= 128 takes the
     weight-streaming kernel (split-K in clusters, every row padding 16..128), larger shapes the 128x128
@@ -416,7 +417,8 @@ def test_fused_residual_add(cuda_device, shape, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(128, 128, 64), (300, 264, 200), (512, 2048, 512), (4096, 2048, 1024),
-                                   (1, 128, 192), (8, 5504, 1024), (33, 520, 2112), (64, 1024, 4096), (100, 264, 200)])
+                                   (1, 128, 192), (8, 5504, 1024), (33, 520, 2112), (64, 1024, 4096), (100, 264, 200),
+                                   (128, 5504, 512)])
 def test_fused_swiglu(cuda_device, shape, dtype):
     """C = silu(A.Wg) * (A.Wu) from one GEMM over the column-interleaved [Wg|Wu] weight; decode-shaped
     row counts (M <= 128) go through the weight-streaming kernel's epilogue."""

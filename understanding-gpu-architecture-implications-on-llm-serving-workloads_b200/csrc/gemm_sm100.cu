@@ -546,6 +546,13 @@ int launch_generic(const void* A, const void* B, void* C, int M, int N, int K, i
 
 using namespace b200k;
 
+// 65..128 rows against a weight of 75 or more 128-column slabs (N >= 9600: the slabs alone nearly fill
+// the GPU, no split-K either way): the 128x128 tile kernel is measured 4-5 % ahead of the weight-streaming
+// kernel (graph-replayed, bf16, K = 4096: N = 11008 4.79 vs 4.55 TB/s at M = 128, N = 12288 5.09 vs 4.89),
+// whose 16 KB activation tile per stage halves the weight bytes it keeps in flight at these row counts.
+// On narrower weights, where the streaming kernel's split-K fills the GPU, it is up to 2x behind.
+static bool wide_rows_on_tiles(int M, int N) { return M > 64 && (N + 127) / 128 >= 75; }
+
 extern "C" size_t b200k_gemm_workspace_bytes(int M, int N, int K, int variant) {
   (void)M;
   (void)N;
@@ -572,11 +579,13 @@ extern "C" int b200k_gemm(const void* A, const void* B, void* C, int M, int N, i
       const int sms = dev_info().sm_count > 0 ? dev_info().sm_count : 148;
       const long pair_tiles = (long)((M + 255) / 256) * ((N + 255) / 256);
       const long tiles256 = (long)((M + 127) / 128) * ((N + 255) / 256);
-      if (M <= 128)
+      if (M <= 128 && !wide_rows_on_tiles(M, N))
         // weight streaming (split-K inside clusters where the slabs alone do not fill the GPU): measured
         // ahead of the 128-column tiles without split-K on every width from 4096 to 32000 columns for
         // M <= 64 (up to +25 %), within -4 % .. +10 % of them for M = 100..128
         variant = B200K_GEMM_SKINNY;
+      else if (M <= 128)
+        variant = B200K_GEMM_1CTA_N128;
       else if (pair_tiles >= sms / 2)
         variant = B200K_GEMM_2CTA;  // at least one full wave of 256x256 pair tiles
       else
@@ -654,7 +663,7 @@ extern "C" int b200k_gemm_fused(const void* A, const void* B, void* C, const voi
   const bool big = pair_tiles >= sms / 2;
   const bool bf16 = dtype == B200K_BF16;
   // decode-shaped calls stream the weight like the plain skinny GEMM (same rule as b200k_gemm's AUTO)
-  if (M <= 128)
+  if (M <= 128 && !wide_rows_on_tiles(M, N))
     return launch_skinny(A, B, C, M, N, K, lda, ldb, ldc, bf16, stream, epilogue, R, ldr);
 #define B200K_FUSED(EP)                                                                                       \
   (big ? (bf16 ? launch_tc<2, 256, 6, true, EP>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream, R, ldr)         \
