@@ -72,13 +72,6 @@ def decode_workspace(B: int, Hq: int, Hkv: int, Sq: int, Skv: int, D: int, num_s
     return torch.empty(max(int(n), 16), dtype=torch.uint8, device=device)
 
 
-def decode_static_fits(B: int, Hq: int, Hkv: int, Sq: int, Skv: int, D: int) -> bool:
-    """Whether the allocation-free decode entry point can take this problem with the split count left
-    to the library: always (the count is lowered until the partials fit the built-in scratch array;
-    one split per sequence keeps no partials)."""
-    return True
-
-
 def fmha_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_lens: torch.Tensor | None = None,
                 num_splits: int = 0, scale: float | None = None, out: torch.Tensor | None = None,
                 workspace: torch.Tensor | None = None, static_scratch: bool = False) -> torch.Tensor:

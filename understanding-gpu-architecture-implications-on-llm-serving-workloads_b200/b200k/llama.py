@@ -209,8 +209,7 @@ class SyntheticLlama:
         out[:, :S] = prompt
         st = {"tok": torch.zeros((B, 1), dtype=torch.long, device=dev), "pos": torch.zeros(1, dtype=torch.long, device=dev),
               "lens": torch.zeros(B, dtype=torch.int32, device=dev), "out": out,
-              "static_scratch": self.lib and fmha.decode_static_fits(B, self.cfg.n_heads, self.cfg.n_kv_heads, 1,
-                                                                      S + gen_len, self.cfg.head_dim)}
+              "static_scratch": bool(self.lib)}  # the allocation-free entry point takes any size with its own split choice
 
         def reset(first_tok):
             st["tok"].copy_(first_tok)
