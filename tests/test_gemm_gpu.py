@@ -42,7 +42,7 @@ def _inputs(M, N, K, dtype, seed=0, std_b=1.0):
     return a, b
 
 
-@pytest.mark.parametrize("variant", [1, 2, 4])
+@pytest.mark.parametrize("variant", [1, 2, 4, 6, 7])
 def test_structured_identity(cuda_device, variant):
     """A = I picks rows of B; B = I picks columns of A: catches operand-layout
     (descriptor / swizzle / major-ness) mistakes exactly, with no tolerance."""
@@ -61,7 +61,7 @@ def test_structured_identity(cuda_device, variant):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("variant", [0, 1, 2, 4, 5])
+@pytest.mark.parametrize("variant", [0, 1, 2, 4, 5, 6, 7])
 @pytest.mark.parametrize("shape", [(128, 256, 64), (128, 128, 128), (256, 512, 256), (1024, 1024, 1024),
                                    (384, 768, 4096)])
 def test_parity_aligned(cuda_device, shape, variant, dtype):
@@ -72,7 +72,7 @@ def test_parity_aligned(cuda_device, shape, variant, dtype):
     assert err <= TOL, err
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2, 4])
+@pytest.mark.parametrize("variant", [0, 1, 2, 4, 6, 7])
 @pytest.mark.parametrize("shape", [(1, 8, 8), (7, 72, 40), (63, 136, 72), (65, 264, 200), (129, 520, 1000),
                                    (16, 4096, 4096), (300, 11008, 136)])
 def test_parity_ragged_edges(cuda_device, shape, variant):
@@ -373,7 +373,7 @@ def test_large_m_partly_filled_last_tile(cuda_device, N):
     ws = w[:, 2816:2816 + N]          # a view into the wider weight, as the sharding produces it
     ref = oracle.gemm_ref(a.cpu(), ws.cpu())
     first = None
-    for variant in (0, 2, 1, 4, 6):
+    for variant in (0, 2, 1, 4, 6, 7):
         for rep in range(2):
             c = gemm.gemm(a, ws, variant=variant)
             host = c.cpu().float()

@@ -5,7 +5,7 @@ import torch
 
 from . import _lib
 
-AUTO, ONE_CTA, TWO_CTA, SKINNY, ONE_CTA_N128, GENERIC, TWO_CTA_N128 = 0, 1, 2, 3, 4, 5, 6
+AUTO, ONE_CTA, TWO_CTA, SKINNY, ONE_CTA_N128, GENERIC, TWO_CTA_N128, ONE_CTA_N64 = 0, 1, 2, 3, 4, 5, 6, 7
 
 _DTYPES = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
 

@@ -251,7 +251,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // -------------------------------- epilogue --------------------------------
     const int ew = warp & 3;  // TMEM lane quadrant this warp may read
     uint8_t* stg = staging + ew * 8192;
-    uint32_t it = 0;
+    uint32_t it = 0, chunk_seq = 0;
     bool ok = true;
     for (int t = unit; t < num_tiles && ok; t += num_units, ++it) {
       int mb, nb;
@@ -272,7 +272,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tmem_ld32(taddr, v);
         tmem_ld32(taddr + 32, w);
         tmem_ld_wait();
-        uint8_t* buf = stg + (c & 1) * 4096;
+        // the two staging buffers alternate chunk by chunk ACROSS tiles (a 64-column tile has one chunk)
+        uint8_t* buf = stg + (chunk_seq++ & 1) * 4096;
         const int col0 = nb * BN + c * 64;
         if constexpr (EPI == kEpiAdd) {
           // this thread's row of the residual, 64 columns = 8 chunks of 8 elements
@@ -588,8 +589,14 @@ extern "C" int b200k_gemm(const void* A, const void* B, void* C, int M, int N, i
         variant = B200K_GEMM_1CTA_N128;
       else if (pair_tiles >= sms / 2)
         variant = B200K_GEMM_2CTA;  // at least one full wave of 256x256 pair tiles
-      else
-        variant = tiles256 >= sms ? B200K_GEMM_1CTA : B200K_GEMM_1CTA_N128;
+      else if (tiles256 >= sms)
+        variant = B200K_GEMM_1CTA;
+      else {
+        // small problems: 128x128 tiles, or 128x64 when even those leave more than half of the SMs idle
+        // (1024^3: 64 -> 128 CTAs)
+        const long tiles128 = (long)((M + 127) / 128) * ((N + 127) / 128);
+        variant = 2 * tiles128 <= sms ? B200K_GEMM_1CTA_N64 : B200K_GEMM_1CTA_N128;
+      }
     }
   }
   const bool bf16 = dtype == B200K_BF16;
@@ -609,6 +616,10 @@ extern "C" int b200k_gemm(const void* A, const void* B, void* C, int M, int N, i
       if (!tma_ok) return B200K_EALIGN;
       return bf16 ? launch_tc<2, 128, 8, true>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream)
                   : launch_tc<2, 128, 8, false>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream);
+    case B200K_GEMM_1CTA_N64:
+      if (!tma_ok) return B200K_EALIGN;
+      return bf16 ? launch_tc<1, 64, 8, true>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream)
+                  : launch_tc<1, 64, 8, false>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream);
     case B200K_GEMM_1CTA_N128:
       if (!tma_ok) return B200K_EALIGN;
       return bf16 ? launch_tc<1, 128, 6, true>(A, B, &C, 1, M, N, K, lda, ldb, ldc, stream)
