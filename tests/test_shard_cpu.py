@@ -64,6 +64,17 @@ def _worker(rank, world, port, N, results):
         s, e = slabs[rank]
         ok = torch.equal(full, a @ b) or torch.allclose(full, a @ b, atol=1e-5)
         ok = ok and torch.allclose(local, (a @ b)[:, s:e], atol=1e-5)
+        # the collective's own layout: [ranks, M, widest slab], entry r = C[:, slab_r] (zero-padded)
+        recv = shard.all_gather_slabs(local, slabs)
+        widest = max(e1 - s1 for (s1, e1) in slabs)
+        ok = ok and recv.shape == (world, 16, widest)
+        for r, (s1, e1) in enumerate(slabs):
+            ok = ok and torch.allclose(recv[r, :, :e1 - s1], (a @ b)[:, s1:e1], atol=1e-5)
+            ok = ok and bool((recv[r, :, e1 - s1:] == 0).all())
+        # reassembly into a caller's buffer (one strided copy when all slabs have one width)
+        out = torch.full((16, N), float("nan"))
+        got = shard.all_gather_columns(local, slabs, out=out)
+        ok = ok and got is out and torch.allclose(out, a @ b, atol=1e-5)
         results[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
