@@ -51,8 +51,9 @@ enum {
   B200K_GEMM_1CTA_N128 = 4, /* 128x128x64 tiles: more CTAs for small problems */
   B200K_GEMM_GENERIC = 5,   /* CUDA-core kernel without alignment rules (any M, N, K, ld) */
   B200K_GEMM_2CTA_N128 = 6, /* 256x128x64 tiles on a CTA pair: half-size tiles for problems whose
-                               256x256 tiles would leave most of the last wave of CTA pairs idle
-                               (column slabs of a sharded weight) */
+                               256x256 tiles would leave most of the last round of CTA pairs idle
+                               (column slabs of a sharded weight); AUTO takes it where
+                               rounds x time per tile predicts at least 6 % */
   B200K_GEMM_1CTA_N64 = 7   /* 128x64x64 tiles: twice the CTAs of 128x128 for problems of a few dozen tiles */
 };
 

@@ -562,6 +562,21 @@ extern "C" size_t b200k_gemm_workspace_bytes(int M, int N, int K, int variant) {
   return 0;
 }
 
+// Between the two CTA-pair tile shapes.  The 256 x 256 tile is the faster one per flop (measured 1572 against
+// 1437 TFLOP/s on 8192 x 4096 x 11008), but a problem of few tiles ends in a partly filled last round of the
+// persistent grid; the 256 x 128 tile halves that loss.  Estimated time = rounds x time per tile (a half-width
+// tile takes 0.547 of a full one); the half-width tile is taken where that predicts at least 6 % (measured at
+// M = 8192, K = 4096: N = 1408 0.0783 -> 0.0717 ms, N = 1280 0.0816 -> 0.0760 ms; N = 2688, 2816, 5504, 11008
+// predicted and measured slower).
+static bool half_width_pair_tiles_win(int M, int N, int sms) {
+  const long units = sms / 2 > 0 ? sms / 2 : 1;
+  const long rows = (M + 255) / 256;
+  const long t256 = rows * ((N + 255) / 256), t128 = rows * ((N + 127) / 128);
+  const double e256 = (double)((t256 + units - 1) / units);
+  const double e128 = (double)((t128 + units - 1) / units) * 0.547;
+  return e128 < 0.94 * e256;
+}
+
 extern "C" int b200k_gemm(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
                           int64_t ldc, int dtype, int variant, void* workspace, size_t workspace_bytes,
                           b200k_stream_t stream_) {
@@ -587,8 +602,8 @@ extern "C" int b200k_gemm(const void* A, const void* B, void* C, int M, int N, i
         variant = B200K_GEMM_SKINNY;
       else if (M <= 128)
         variant = B200K_GEMM_1CTA_N128;
-      else if (pair_tiles >= sms / 2)
-        variant = B200K_GEMM_2CTA;  // at least one full wave of 256x256 pair tiles
+      else if (pair_tiles >= sms / 2)  // at least one full wave of 256x256 pair tiles
+        variant = half_width_pair_tiles_win(M, N, sms) ? B200K_GEMM_2CTA_N128 : B200K_GEMM_2CTA;
       else if (tiles256 >= sms)
         variant = B200K_GEMM_1CTA;
       else {
