@@ -32,6 +32,9 @@
 #include <cuda_fp16.h>
 #include <math.h>
 #include <stdlib.h>
+#ifdef B200K_FMHA_STAMPS
+#include <stdio.h>
+#endif
 
 #include "host_common.h"
 #include "ptx.cuh"
@@ -57,6 +60,24 @@ static_assert(256 * kSoftmaxRegs + 128 * kAuxRegs <= kFmhaThreads * launch_regs(
 #ifndef B200K_FMHA_MAX_CHAINS
 #define B200K_FMHA_MAX_CHAINS 4  // independent dependency chains of the row maximum (4 or 8)
 #endif
+// Cycle stamps of the softmax threads' phases (-DB200K_FMHA_STAMPS: a diagnostic build of the one-item kernel;
+// one CTA prints, for thread 0 of each softmax group, the cycles per key block it spent in each phase).
+// Without the macro every call is empty.
+struct PhaseStamps {
+#ifdef B200K_FMHA_STAMPS
+  long long acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  long long last = 0;
+  __device__ __forceinline__ void start() { last = clock64(); }
+  __device__ __forceinline__ void mark(int i) {
+    const long long t = clock64();
+    acc[i] += t - last;
+    last = t;
+  }
+#else
+  __device__ __forceinline__ void start() {}
+  __device__ __forceinline__ void mark(int) {}
+#endif
+};
 // P is handed to the MMA warp in kPParts pieces (1, 2 or 4) of 128 / kPParts keys, so that the PV
 // product of the first pieces runs while the softmax group still exponentiates the later ones.
 constexpr int kPParts = B200K_FMHA_P_PARTS;
@@ -222,13 +243,14 @@ __device__ __forceinline__ bool softmax_block(uint32_t s_tmem, uint32_t p_tmem, 
                                               bool masked, int lim, float sc, float& m_use, float& l,
                                               uint64_t* p_part_i, uint64_t* p_ready_i, uint64_t* s_free_i,
                                               bool signal_s_free, uint64_t* p_free_i, bool wait_p_free,
-                                              uint32_t p_free_phase) {
+                                              uint32_t p_free_phase, PhaseStamps& stamps) {
   uint32_t s[128];
   tmem_ld32(s_tmem + 0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
   tmem_ld32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
   tmem_ld32(s_tmem + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
   tmem_ld32(s_tmem + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
   tmem_ld_wait();
+  stamps.mark(1);  // S row in registers
   bool ok = true;
   if constexpr (SPLITP) {
     if (signal_s_free) {  // the row is in registers: the next block's scores may overwrite these columns
@@ -343,12 +365,17 @@ __device__ __forceinline__ bool softmax_block(uint32_t s_tmem, uint32_t p_tmem, 
       rescale_to(m_new);
     }
   }
+  stamps.mark(2);  // mask, row maximum, vote (and the rare rescale)
   uint64_t sum_a = f2pack(0.f, 0.f), sum_b = f2pack(0.f, 0.f);
 #pragma unroll
   for (int qt = 0; qt < 4; ++qt) {
     uint32_t pk[16];
     quarter(qt, pk, sum_a, sum_b);
-    if (qt == 0) wait_prev_pv();  // the previous block's P has been consumed
+    if (qt == 0) {
+      stamps.mark(3);  // first quarter of the exponentials
+      wait_prev_pv();  // the previous block's P has been consumed
+      stamps.mark(4);  // (separate P columns) wait for the previous block's PV
+    }
     tmem_st16(p_tmem + qt * 16, pk);
     // hand the finished piece to the MMA warp (the last piece goes through p_ready below)
     if (qt < 3 && (qt + 1) % (4 / kPParts) == 0) {
@@ -360,6 +387,7 @@ __device__ __forceinline__ bool softmax_block(uint32_t s_tmem, uint32_t p_tmem, 
   tmem_st_wait();
   tc_fence_before();
   mbar_arrive(p_ready_i);
+  stamps.mark(5);  // the other three quarters, P stores, hand-over
   if constexpr (!SUMTC) {
     float a, b;
     f2unpack(add2(sum_a, sum_b), a, b);
@@ -668,6 +696,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       float m_use = -INFINITY;
       float l = 0.f;
       bool ok = true;
+      PhaseStamps stamps;
+      stamps.start();
       for (int j = 0; j < nb[i]; ++j) {
         if (!mbar_wait(&s_full[i], j & 1)) {
           if (lane == 0) report_timeout(p.status, KID_FMHA, ROLE_SOFTMAX);
@@ -675,16 +705,23 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           break;
         }
         tc_fence_after();
+        stamps.mark(0);  // wait for S
         const int k0 = j * kTile;
         if (!softmax_block<D, BF16, EMU, kSumTc, SPLITP>(
                 s_tmem, p_tmem, o_tmem, j == 0, k0 + kTile - 1 > tile_min_lim, lim_row - k0, sc, m_use, l, &p_part[i],
-                &p_ready[i], &s_free[i], j + 1 < nb[i], &p_free[i], j > 0, (uint32_t)((j - 1) & 1))) {
+                &p_ready[i], &s_free[i], j + 1 < nb[i], &p_free[i], j > 0, (uint32_t)((j - 1) & 1), stamps)) {
           if (lane == 0) report_timeout(p.status, KID_FMHA, ROLE_SOFTMAX);
           ok = false;
           break;
         }
       }
 
+#ifdef B200K_FMHA_STAMPS
+      if (blockIdx.x == gridDim.x / 2 && (threadIdx.x & 127) == 0 && nb[i] > 0)
+        printf("stamps tile %d blocks %d: wait_S %lld ld %lld max %lld exp_q0 %lld wait_pv %lld exp_rest %lld (cycles per block)\n", i,
+               nb[i], stamps.acc[0] / nb[i], stamps.acc[1] / nb[i], stamps.acc[2] / nb[i], stamps.acc[3] / nb[i],
+               stamps.acc[4] / nb[i], stamps.acc[5] / nb[i]);
+#endif
       // ------------------------------ epilogue ------------------------------
       if (ok && nb[i] > 0) {
         if (!mbar_wait(&o_full[i], 0)) {
@@ -1133,6 +1170,7 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       const int tile_min_lim = p.causal ? min(it.q0[i] + off, p.kv_len - 1) : p.kv_len - 1;
       float m_use = -INFINITY;
       float l = 0.f;
+      PhaseStamps stamps;  // (the diagnostic build prints from the one-item kernel only)
       for (int j = 0; j < it.nb[i]; ++j) {
         if (!mbar_wait(&s_full[i], sn & 1)) {
           if (lane == 0) report_timeout(p.status, KID_FMHA, ROLE_SOFTMAX);
@@ -1144,7 +1182,7 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         const int k0 = j * kTile;
         if (!softmax_block<D, BF16, EMU, kSumTc, SPLITP>(
                 s_tmem, p_tmem, o_tmem, j == 0, k0 + kTile - 1 > tile_min_lim, lim_row - k0, sc, m_use, l, &p_part[i],
-                &p_ready[i], &s_free[i], j + 1 < it.nb[i], &p_free[i], j > 0, pfn & 1)) {
+                &p_ready[i], &s_free[i], j + 1 < it.nb[i], &p_free[i], j > 0, pfn & 1, stamps)) {
           if (lane == 0) report_timeout(p.status, KID_FMHA, ROLE_SOFTMAX);
           ok = false;
           break;
