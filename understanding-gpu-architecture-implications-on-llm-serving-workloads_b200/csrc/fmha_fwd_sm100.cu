@@ -80,8 +80,14 @@ struct PhaseStamps {
 };
 // P is handed to the MMA warp in kPParts pieces (1, 2 or 4) of 128 / kPParts keys, so that the PV
 // product of the first pieces runs while the softmax group still exponentiates the later ones.
-constexpr int kPParts = B200K_FMHA_P_PARTS;
-static_assert(kPParts == 1 || kPParts == 2 || kPParts == 4, "P is handed over in 1, 2 or 4 pieces");
+// Two pieces by default; four in the one-item kernel at d = 128, where only the last piece's PV product (128
+// instead of 256 tensor-pipe cycles) then stands between a group's hand-over and the next block's QK^T: measured
+// +1..2 % at s = 8192 (full 1182-1197 -> 1202-1239 TFLOP/s, causal 1112-1114 -> 1121-1133, three alternating runs);
+// the persistent kernel (within +-1 %) and d = 64 (-2 %) keep two.
+static_assert(B200K_FMHA_P_PARTS == 1 || B200K_FMHA_P_PARTS == 2 || B200K_FMHA_P_PARTS == 4,
+              "P is handed over in 1, 2 or 4 pieces");
+template <int D, bool PERSISTENT>
+constexpr int kPPartsOf = (D == 128 && !PERSISTENT && B200K_FMHA_P_PARTS == 2) ? 4 : B200K_FMHA_P_PARTS;
 
 // Row sums on the tensor pipe (head dimension 64 only, where TMEM has 128 spare columns): every V
 // stage is followed by a 64-wide box filled with ones, the PV product runs with N = D + 16, and the 16
@@ -238,7 +244,7 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
 //   group releases the S columns (`s_free_i`, when another block follows), and it waits for the previous
 //   block's PV product (`p_free_i`, parity `p_free_phase`, when `wait_p_free`) before it rescales O or
 //   stores the first P.  Returns false if that wait ran out.
-template <int D, bool BF16, int EMU, bool SUMTC, bool SPLITP>
+template <int D, bool BF16, int EMU, bool SUMTC, bool SPLITP, int kPParts>
 __device__ __forceinline__ bool softmax_block(uint32_t s_tmem, uint32_t p_tmem, uint32_t o_tmem, bool first,
                                               bool masked, int lim, float sc, float& m_use, float& l,
                                               uint64_t* p_part_i, uint64_t* p_ready_i, uint64_t* s_free_i,
@@ -581,6 +587,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       };
       // PV_i of block j as the pieces of P arrive; false if a wait ran out
       auto pv_block = [&](int i, int stage, int j) {
+        constexpr int kPParts = kPPartsOf<D, false>;
         constexpr int kStepsPerPart = kTile / 16 / kPParts;
 #pragma unroll
         for (int part = 0; part + 1 < kPParts; ++part) {
@@ -707,7 +714,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_after();
         stamps.mark(0);  // wait for S
         const int k0 = j * kTile;
-        if (!softmax_block<D, BF16, EMU, kSumTc, SPLITP>(
+        if (!softmax_block<D, BF16, EMU, kSumTc, SPLITP, kPPartsOf<D, false>>(
                 s_tmem, p_tmem, o_tmem, j == 0, k0 + kTile - 1 > tile_min_lim, lim_row - k0, sc, m_use, l, &p_part[i],
                 &p_ready[i], &s_free[i], j + 1 < nb[i], &p_free[i], j > 0, (uint32_t)((j - 1) & 1), stamps)) {
           if (lane == 0) report_timeout(p.status, KID_FMHA, ROLE_SOFTMAX);
@@ -1020,6 +1027,7 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
           fail();
           return;
         }
+        constexpr int kPParts = kPPartsOf<D, true>;
         constexpr int kStepsPerPart = kTile / 16 / kPParts;
 #pragma unroll
         for (int part = 0; part + 1 < kPParts; ++part) {
@@ -1180,7 +1188,7 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         ++sn;
         tc_fence_after();
         const int k0 = j * kTile;
-        if (!softmax_block<D, BF16, EMU, kSumTc, SPLITP>(
+        if (!softmax_block<D, BF16, EMU, kSumTc, SPLITP, kPPartsOf<D, true>>(
                 s_tmem, p_tmem, o_tmem, j == 0, k0 + kTile - 1 > tile_min_lim, lim_row - k0, sc, m_use, l, &p_part[i],
                 &p_ready[i], &s_free[i], j + 1 < it.nb[i], &p_free[i], j > 0, pfn & 1, stamps)) {
           if (lane == 0) report_timeout(p.status, KID_FMHA, ROLE_SOFTMAX);
