@@ -32,10 +32,19 @@ Pinning
 The reference ships no golden vectors or known-answer files for these paths
 (its correct.py scripts compare against torch on the GPU at run time, and the
 FMHA one currently compares against raw QK^T, kernels/fmha/test/correct.py:52).
-The oracle is therefore pinned against outputs of the reference test's own
-oracle functions (torch `a @ b` and `F.scaled_dot_product_attention` with
-`repeat_kv`) generated in the build container with the reference's seeds and
-shapes and committed under tests/golden/ (tests/golden/make_golden.py).
+The oracle is pinned to the reference itself in two ways:
+* tests/golden/: outputs of the reference's own oracle function, `torch_attn`
+  IMPORTED from kernels/fmha/test/perf.py:10-24 (and `a @ b`,
+  kernels/gemm/test/correct.py:9-16), generated in the build container with the
+  reference's seeds and shapes by tests/golden/make_golden.py;
+  tests/test_oracle_cpu.py holds the oracle to them on CPU;
+* the reference's own CUDA rungs (finegemm_8 / _11, finefmha_2 / _4), compiled
+  from the reference's sources by oracle/build_ref_ladder.py into oracle/_ref/
+  and run in a child process by oracle/run_ref_check.py on the reference's
+  check inputs (kernels/gemm/test/correct.py:5-16, kernels/fmha/test/correct.py:
+  26-47): tests/test_reference_pin_gpu.py requires oracle <-> reference within
+  the reference's tolerances and library <-> oracle within the stated ones on
+  the same tensors.
 """
 from __future__ import annotations
 
