@@ -103,6 +103,31 @@ def test_parity_cross_lengths(cuda_device, causal):
     _check(q2, k2, v2, causal, cuda_device)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("shape", [(257, 257, 173), (128, 258, 108), (520, 520, 25), (256, 256, 64), (200, 140, 31)])
+def test_rows_without_a_visible_key_are_zero(cuda_device, shape, D, dtype):
+    """Causal with fewer valid keys than queries (diagonal aligned bottom-right to kv_len): the first
+    Sq - kv_len rows see no key and are zero, also when they share a 128-row tile with rows that do see
+    keys - then the tile's blocks run, every score of such a row is masked, and nothing of V may leak into
+    it.  (In bf16 the clamped 2^-125 of an emulated exponential survives the rounding of P; a row's
+    denominator made of those once turned its output into a mean of V.)  All kernel variants."""
+    from b200k import fmha, inputs
+    Sq, Skv, kv_len = shape
+    q, k, v = inputs.fmha_inputs(2, 4, 2, Sq, Skv, D, dtype, seed=31 + Sq)
+    k[:, :, kv_len:] = float("nan")
+    v[:, :, kv_len:] = float("nan")
+    ref, absref = _refs(q, k, v, True, kv_len)
+    dead = max(0, Sq - kv_len)
+    assert dead > 0 and float(ref[:, :, :dead].abs().max()) == 0.0
+    for variant in (0, 1, 2, 3, 11, 12, 13):
+        o = fmha.fmha_fwd(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), causal=True, kv_len=kv_len,
+                          variant=variant)
+        torch.cuda.synchronize()
+        assert float(o[:, :, :dead].float().abs().max()) == 0.0, variant
+        _assert_close(o, ref, absref=absref)
+
+
 def test_bshd_storage_is_zero_copy(cuda_device):
     """Tensors stored [B,S,H,D] and viewed [B,H,S,D] are consumed through strides."""
     from b200k import fmha, inputs

@@ -745,7 +745,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             l = __uint_as_float(t);
           }
         }
-        const float inv = l > 0.f ? 1.f / l : 0.f;
+        // A row that saw no visible key in any block (m still -inf) is zero.  Its l is not: a masked score's
+        // emulated exponential is clamped to 2^-125, which a bf16 P keeps (fp16 flushes it), so l and O hold
+        // a mean of V scaled by 2^-125 that the division would blow up to a mean of V.
+        const float inv = (l > 0.f && m_use != -INFINITY) ? 1.f / l : 0.f;
         uint8_t* stage = smem + L::kQOff + i * L::kTileBytes;  // Q_i is no longer read
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
@@ -1215,7 +1218,8 @@ fmha_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
           l = __uint_as_float(t);
         }
       }
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      // (a row without any visible key is zero: see the one-item kernel's epilogue)
+      const float inv = (l > 0.f && m_use != -INFINITY) ? 1.f / l : 0.f;
 #pragma unroll
       for (int hb = 0; hb < kDBoxes; ++hb) {
         // 64 columns of O at a time: TMEM -> registers -> staging buffer -> TMA store
