@@ -130,6 +130,9 @@ def preflight_agree(description, group=None, timeout_s: float = 30.0) -> None:
 
 def sharded_gemm(a: torch.Tensor, b_full: torch.Tensor, gather: bool, matmul, group=None):
     """Rank-local slab of a @ b_full (and the gathered full product when `gather`).
+    With the library GEMM the gathered product equals the unsharded one bit for bit for more than 128
+    rows (the tile kernels sum every output element in one order); up to 128 rows the weight-streaming
+    kernel splits K according to the number of slabs, so the two agree to rounding only.
     `matmul(a, b_slab)` is the local kernel (the library GEMM on GPU; torch.matmul in
     the CPU tests of this host logic)."""
     world = dist.get_world_size(group)
